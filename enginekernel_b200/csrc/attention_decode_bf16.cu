@@ -58,7 +58,8 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
                              const int* positions, const int* token_slot,
                              PagedKV cache, int n_q_heads, int row_blocks, float scale_log2,
                              int window, int n_splits, int keys_per_split,
-                             float* __restrict__ part_acc, float* __restrict__ part_ml) {
+                             float* __restrict__ part_acc, float* __restrict__ part_ml,
+                             float sink_log2) {
   constexpr int D = DCH * 32;
   extern __shared__ float smem[];              // [warps][16][D] accumulators, then [warps][16][2]
   float* o_s = smem;
@@ -232,6 +233,8 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
     }
     const int head = head0 + r;
     if (n_splits == 1) {
+      // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
+      if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);
       out[((size_t)t * n_q_heads + head) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     } else {
       const size_t pi = ((size_t)t * n_q_heads + head) * n_splits + split;
@@ -248,7 +251,7 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
 __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
                                                 const float* part_acc,
                                                 const float* part_ml, int n_q_heads,
-                                                int head_dim, int n_splits) {
+                                                int head_dim, int n_splits, float sink_log2) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
@@ -258,6 +261,7 @@ __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
   float l = 0.f;
   for (int s = 0; s < n_splits; ++s)
     if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * exp2f(ml[2 * s] - m);
+  if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);      // the sink, counted once
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float acc = 0.f;
@@ -272,7 +276,7 @@ template <int DCH>
 static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                       const int* token_slot, PagedKV cache, int n_tokens, int n_q_heads,
                       float scale, int window, int n_splits, int keys_per_split, float* part_acc,
-                      float* part_ml, cudaStream_t stream) {
+                      float* part_ml, float sink, cudaStream_t stream) {
   constexpr int D = DCH * 32;
   const int group = n_q_heads / cache.heads;
   const int row_blocks = (group + 15) / 16;
@@ -291,24 +295,27 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
   cudaError_t e = launch_pdl(attention_decode_bf16_kernel<DCH>, grid, dim3(kDecWarps * 32), smem,
                              stream, out, q, q_row_stride, positions, token_slot, cache, n_q_heads,
                              row_blocks, scale * 1.4426950408889634f, window, n_splits,
-                             keys_per_split, part_acc, part_ml);
+                             keys_per_split, part_acc, part_ml, sink * 1.4426950408889634f);
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
   return (int)launch_pdl(attention_decode_combine_kernel, cgrid, dim3(64), 0, stream, out,
-                         (const float*)part_acc, (const float*)part_ml, n_q_heads, D, n_splits);
+                         (const float*)part_acc, (const float*)part_ml, n_q_heads, D, n_splits,
+                         sink * 1.4426950408889634f);
 }
 
 }  // namespace ek
 
 // head_dim must be a multiple of 32 (up to 256); keys_per_split a multiple of 16, or 0 to cut
-// each token's visible keys into n_splits equal parts.
+// each token's visible keys into n_splits equal parts.  `sink`: score of a key without a value
+// that every query also sees (one more term in the softmax denominator); -INFINITY for none.
 EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_stride,
                                        const int* positions, const int* token_slot,
                                        const void* k_pages, const void* v_pages,
                                        const int* block_table, int table_stride, int n_tokens,
                                        int n_q_heads, int n_kv_heads, int head_dim, float scale,
                                        int window, int n_splits, int keys_per_split,
-                                       float* part_acc, float* part_ml, cudaStream_t stream) {
+                                       float* part_acc, float* part_ml, float sink,
+                                       cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if (head_dim % 32 || head_dim < 32 || head_dim > 256 || n_kv_heads <= 0 ||
@@ -320,7 +327,7 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
   case DCH:                                                                                       \
     return launch_dch<DCH>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cache, \
                            n_tokens, n_q_heads, scale, window, n_splits, keys_per_split, part_acc, \
-                           part_ml, stream);
+                           part_ml, sink, stream);
   switch (head_dim / 32) {
     EK_CASE(1) EK_CASE(2) EK_CASE(3) EK_CASE(4) EK_CASE(5) EK_CASE(6) EK_CASE(7) EK_CASE(8)
   }
@@ -392,5 +399,5 @@ EK_EXPORT int ek_attention_decode_bf16_noalloc(void* out, const void* q, int q_r
   return ek_attention_decode_bf16(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,
                                   block_table, table_stride, n_tokens, n_q_heads, n_kv_heads,
                                   head_dim, scale, window, n_splits, keys_per_split, part_acc,
-                                  part_ml, stream);
+                                  part_ml, -INFINITY, stream);
 }

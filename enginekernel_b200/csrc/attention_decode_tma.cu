@@ -69,7 +69,7 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
                             const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* block_table,
                             int table_stride, int n_kv_heads, int n_q_heads, float scale_log2,
-                            int window, int* status) {
+                            int window, int* status, float sink_log2) {
   constexpr int DB = D / 64;                       // 64-wide (128-byte) blocks of the head dimension
   constexpr uint32_t kSub = EK_PAGE * 128;         // one [64 keys x 64 dims] sub-tile: 8 KB
   constexpr uint32_t kStage = 2 * DB * kSub;       // K tile + V tile
@@ -302,6 +302,8 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
         }
       }
       if (n_splits == 1) {
+        // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
+        if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);
         out[((size_t)t * n_q_heads + head0 + r) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
       } else {
         const int owner = idx / run;
@@ -336,6 +338,7 @@ attention_decode_tma_kernel(bf16* __restrict__ out, const bf16* q, int q_row_str
           o += recv_o[sp * run + slot] * f;
         }
       }
+      if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);   // the sink, counted once
       out[((size_t)t * n_q_heads + head0) * D + idx] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
   }
@@ -348,7 +351,7 @@ static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* posi
                      const int* token_slot, const void* k_pages, const void* v_pages,
                      long long page_rows, const int* block_table, int table_stride, int n_tokens,
                      int n_q_heads, int n_kv_heads, float scale, int window, int n_splits, int* status,
-                     cudaStream_t stream) {
+                     float sink, cudaStream_t stream) {
   constexpr int STAGES = (D == 128 ? 3 : 6) * (DEEP ? 2 : 1);
   constexpr int DB = D / 64;
   constexpr size_t smem = 1024 + (size_t)STAGES * 2 * DB * EK_PAGE * 128 + 2 * STAGES * 8 +
@@ -397,10 +400,12 @@ static int launch_dt(bf16* out, const bf16* q, int q_row_stride, const int* posi
     return (int)launch_pdl_cluster_x(kernel, grid, dim3(kDtThreads), smem, stream, n_splits, out, q,
                                      q_row_stride, positions, token_slot, mk, mv, block_table,
                                      table_stride, n_kv_heads, n_q_heads,
-                                     scale * 1.4426950408889634f, window, status);
+                                     scale * 1.4426950408889634f, window, status,
+                         sink * 1.4426950408889634f);
   return (int)launch_pdl(kernel, grid, dim3(kDtThreads), smem, stream, out, q, q_row_stride, positions,
                          token_slot, mk, mv, block_table, table_stride, n_kv_heads, n_q_heads,
-                         scale * 1.4426950408889634f, window, status);
+                         scale * 1.4426950408889634f, window, status,
+                         sink * 1.4426950408889634f);
 }
 
 }  // namespace ek
@@ -412,10 +417,10 @@ EK_EXPORT int ek_attention_decode_tma_max_splits(int head_dim) {
   int clusters = 0;
   if (head_dim == 64)
     clusters = launch_dt<64, false, true>(nullptr, nullptr, 0, nullptr, nullptr, &clusters, &clusters, 64,
-                                          nullptr, 0, 1, 1, 1, 1.f, 0, 1, nullptr, nullptr);
+                                          nullptr, 0, 1, 1, 1, 1.f, 0, 1, nullptr, -INFINITY, nullptr);
   else if (head_dim == 128)
     clusters = launch_dt<128, false, true>(nullptr, nullptr, 0, nullptr, nullptr, &clusters, &clusters, 64,
-                                           nullptr, 0, 1, 1, 1, 1.f, 0, 1, nullptr, nullptr);
+                                           nullptr, 0, 1, 1, 1, 1.f, 0, 1, nullptr, -INFINITY, nullptr);
   else
     return 0;
   return clusters >= 1 ? kDtMaxSplits : kDtPortableSplits;
@@ -423,13 +428,16 @@ EK_EXPORT int ek_attention_decode_tma_max_splits(int head_dim) {
 
 // head_dim 64 or 128; at most 16 query heads a KV head; 1 to 16 splits (each takes whole pages of
 // the token's visible range); q rows 4-byte aligned; n_pages = pages in k_pages / v_pages
-// ([pages, kv heads, 64, head_dim]); `status` is one int on the device.
+// ([pages, kv heads, 64, head_dim]); `status` is one int on the device.  `sink`: score of a key
+// without a value that every query also sees (one more term in the softmax denominator);
+// -INFINITY for none.
 EK_EXPORT int ek_attention_decode_tma(void* out, const void* q, int q_row_stride,
                                       const int* positions, const int* token_slot,
                                       const void* k_pages, const void* v_pages, int n_pages,
                                       const int* block_table, int table_stride, int n_tokens,
                                       int n_q_heads, int n_kv_heads, int head_dim, float scale,
-                                      int window, int n_splits, int* status, cudaStream_t stream) {
+                                      int window, int n_splits, int* status, float sink,
+                                      cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || n_kv_heads <= 0 || n_q_heads % n_kv_heads ||
@@ -442,7 +450,7 @@ EK_EXPORT int ek_attention_decode_tma(void* out, const void* q, int q_row_stride
 #define EK_DT(D_, DEEP_)                                                                          \
   return launch_dt<D_, DEEP_>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,     \
                               k_pages, v_pages, page_rows, block_table, table_stride, n_tokens,   \
-                              n_q_heads, n_kv_heads, scale, window, n_splits, status, stream)
+                              n_q_heads, n_kv_heads, scale, window, n_splits, status, sink, stream)
   if (head_dim == 64) {
     if (deep) EK_DT(64, true);
     EK_DT(64, false);

@@ -3,6 +3,8 @@
 // (token, query head, key split) walks the keys the token may see:
 //     lo = max(0, pos - window + 1) (window <= 0: 0)  ...  pos
 // with a running maximum and sum (online softmax) so that no score row is stored.
+// An optional sink - a key without a value whose fixed score `sink` every query sees - adds
+// exp(sink) to the softmax denominator once per (token, head); -INFINITY switches it off.
 // It serves whole prompts, chunks and single decoded tokens alike, since each token
 // carries its own position and slot; the faster bfloat16 kernels in attention_bf16.cu
 // cover the common head sizes, this one covers everything and is the 32-bit path.
@@ -24,6 +26,10 @@ template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ row,
                                                 const float* __restrict__ q, int d) {
   float s = 0.f;
+  if (d % 4) {                                 // rows that do not start on 16-byte boundaries
+    for (int i = 0; i < d; ++i) s += row[i] * q[i];
+    return s;
+  }
   const float4* r4 = reinterpret_cast<const float4*>(row);
   for (int i = 0; i < d / 4; ++i) {
     const float4 v = r4[i];
@@ -36,6 +42,10 @@ template <>
 __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ row,
                                                const float* __restrict__ q, int d) {
   float s = 0.f;
+  if (d % 8) {                                 // rows that do not start on 16-byte boundaries
+    for (int i = 0; i < d; ++i) s += __bfloat162float(row[i]) * q[i];
+    return s;
+  }
   const uint4* r4 = reinterpret_cast<const uint4*>(row);
   for (int i = 0; i < d / 8; ++i) {
     const uint4 v = r4[i];
@@ -55,7 +65,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          const int* __restrict__ token_slot, PagedKV cache,
                                          int n_q_heads, float scale, int window, int n_splits,
                                          int keys_per_split, float* __restrict__ part_acc,
-                                         float* __restrict__ part_ml) {
+                                         float* __restrict__ part_ml, float sink) {
   __shared__ float q_s[EK_MAX_HEAD_DIM];
   __shared__ float p_s[kAttnThreads];
   __shared__ size_t voff_s[kAttnThreads];
@@ -117,6 +127,8 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 
   if (n_splits == 1) {
     T* orow = out + ((size_t)t * n_q_heads + h) * d;
+    // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
+    if (sink > -INFINITY && l > 0.f) l += expf(sink - m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
     if (tid < d) orow[tid] = from_f<T>(acc0 * inv);
     if (tid + kAttnThreads < d) orow[tid + kAttnThreads] = from_f<T>(acc1 * inv);
@@ -135,7 +147,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 template <typename T>
 __global__ void attention_combine_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml, int n_q_heads,
-                                         int head_dim, int n_splits) {
+                                         int head_dim, int n_splits, float sink) {
   const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
   const float* ml = part_ml + 2 * th * n_splits;
   float m = -INFINITY;
@@ -143,6 +155,7 @@ __global__ void attention_combine_kernel(T* __restrict__ out, const float* __res
   float l = 0.f;
   for (int s = 0; s < n_splits; ++s)
     if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
+  if (sink > -INFINITY && l > 0.f) l += expf(sink - m);                 // the sink, counted once
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
     float acc = 0.f;
@@ -157,9 +170,10 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
                   const int* token_slot, const void* k_pages, const void* v_pages,
                   const int* block_table, int table_stride, int n_tokens, int n_q_heads,
                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
-                  int keys_per_split, float* part_acc, float* part_ml, cudaStream_t stream) {
+                  int keys_per_split, float* part_acc, float* part_ml, float sink,
+                  cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || head_dim % 8 || n_kv_heads <= 0 ||
+  if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || n_kv_heads <= 0 ||
       n_q_heads % n_kv_heads || n_q_heads > 65535 || n_splits < 1 || n_splits > 65535 ||
       (n_splits > 1 && (!part_acc || !part_ml || keys_per_split <= 0)))
     return EK_ERR_ARG;
@@ -167,12 +181,12 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
   dim3 grid(n_tokens, n_q_heads, n_splits);
   attention_generic_kernel<T><<<grid, kAttnThreads, 0, stream>>>(
       (T*)out, (const T*)q, q_row_stride, positions, token_slot, cache, n_q_heads, scale, window,
-      n_splits, keys_per_split, part_acc, part_ml);
+      n_splits, keys_per_split, part_acc, part_ml, sink);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
   attention_combine_kernel<T><<<cgrid, 64, 0, stream>>>((T*)out, part_acc, part_ml, n_q_heads,
-                                                        head_dim, n_splits);
+                                                        head_dim, n_splits, sink);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -183,10 +197,12 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
       void* out, const void* q, int q_row_stride, const int* positions, const int* token_slot, \
       const void* k_pages, const void* v_pages, const int* block_table, int table_stride,      \
       int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, float scale, int window,      \
-      int n_splits, int keys_per_split, float* part_acc, float* part_ml, cudaStream_t stream) { \
+      int n_splits, int keys_per_split, float* part_acc, float* part_ml, float sink,           \
+      cudaStream_t stream) {                                                                   \
     return ek::launch<T>(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,        \
                          block_table, table_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, \
-                         scale, window, n_splits, keys_per_split, part_acc, part_ml, stream);  \
+                         scale, window, n_splits, keys_per_split, part_acc, part_ml, sink,     \
+                         stream);                                                              \
   }
 
 EK_INSTANTIATE(f32, float)

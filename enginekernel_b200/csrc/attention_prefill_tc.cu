@@ -74,7 +74,7 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
                             const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* block_table,
                             int table_stride, int n_kv_heads, int n_q_heads, float scale_log2,
-                            int window, int tok_per_tile, int* status) {
+                            int window, int tok_per_tile, int* status, float sink_log2) {
   constexpr int DB = D / 64;                       // 64-wide blocks of the head dimension
   constexpr uint32_t kSub = kFaKeys * 128;         // one [64 x 64] bfloat16 sub-tile: 8 KB
   constexpr uint32_t kTmemCols = 256;
@@ -315,6 +315,8 @@ attention_prefill_tc_kernel(bf16* __restrict__ out, const __grid_constant__ CUte
   const int failed = __syncthreads_or(ok ? 0 : 1);
   if (!failed) {
     if (tid < kFaRows) {                           // whole warps: tcgen05.ld is warp-wide
+      // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
+      if (sink_log2 > -INFINITY && l_run > 0.f) l_run += exp2f(sink_log2 - m_ref);
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const bool wide_out = ((uintptr_t)out & 31) == 0;     // rows of D values are then 32-byte aligned
       const int row = min(r, n_rows - 1);
@@ -443,7 +445,7 @@ template <int D>
 static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int4* tiles, int n_tiles, int n_tokens,
                      const void* k_pages, const void* v_pages, long long page_rows,
                      const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
-                     float scale, int window, int* status, cudaStream_t stream) {
+                     float scale, int window, int* status, float sink, cudaStream_t stream) {
   const int group = n_q_heads / n_kv_heads;
   const int tok_per_tile = kFaRows / group;
   CUtensorMap mq, mk, mv;
@@ -469,7 +471,7 @@ static int launch_fa(bf16* out, const bf16* q, int q_row_stride, const int4* til
   dim3 grid(n_kv_heads, n_tiles);
   return (int)launch_pdl(kernel, grid, dim3(kFaThreads), smem, stream, out, mq, tiles, mk, mv, block_table,
                          table_stride, n_kv_heads, n_q_heads, scale * 1.4426950408889634f, window,
-                         tok_per_tile, status);
+                         tok_per_tile, status, sink * 1.4426950408889634f);
 }
 
 }  // namespace ek
@@ -492,12 +494,14 @@ EK_EXPORT int ek_attention_prefill_tiles(int* tiles, int max_tiles, const int* c
 // head_dim 64 or 128; the group (query heads per KV head) must divide 128; q rows 16-byte
 // aligned; n_pages = number of pages in k_pages / v_pages ([pages, kv heads, 64, head_dim]);
 // `tiles` / n_tiles: the table ek_attention_prefill_tiles made for this step and group size.
+// `sink`: score of a key without a value that every query also sees (one more term in the softmax
+// denominator); -INFINITY for none.
 EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride, const int* tiles,
                                       int n_tiles, int n_tokens,
                                       const void* k_pages, const void* v_pages, int n_pages,
                                       const int* block_table, int table_stride, int n_q_heads,
                                       int n_kv_heads, int head_dim, float scale, int window,
-                                      int* status, cudaStream_t stream) {
+                                      int* status, float sink, cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0 || n_tiles <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || n_kv_heads <= 0 || n_q_heads % n_kv_heads ||
@@ -508,8 +512,8 @@ EK_EXPORT int ek_attention_prefill_tc(void* out, const void* q, int q_row_stride
   if (head_dim == 64)
     return launch_fa<64>((bf16*)out, (const bf16*)q, q_row_stride, (const int4*)tiles, n_tiles, n_tokens,
                          k_pages, v_pages, page_rows, block_table, table_stride,
-                         n_q_heads, n_kv_heads, scale, window, status, stream);
+                         n_q_heads, n_kv_heads, scale, window, status, sink, stream);
   return launch_fa<128>((bf16*)out, (const bf16*)q, q_row_stride, (const int4*)tiles, n_tiles, n_tokens,
                         k_pages, v_pages, page_rows, block_table, table_stride,
-                        n_q_heads, n_kv_heads, scale, window, status, stream);
+                        n_q_heads, n_kv_heads, scale, window, status, sink, stream);
 }

@@ -10,11 +10,14 @@
 
 namespace ek {
 
-// resid[t] = table[ids[t]] * scale (+ pos_table[positions[t]] if the model has learned positions)
+// resid[t] = table[ids[t]] * scale (+ pos_table[positions[t]] if the model has learned positions);
+// with `accumulate` the same is added to what resid[t] holds (a model that feeds its embedding
+// output into the stream again at a later layer).
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
                              const int* ids, int hidden, int vocab, float scale,
-                             const T* __restrict__ pos_table, const int* positions, int max_positions) {
+                             const T* __restrict__ pos_table, const int* positions, int max_positions,
+                             int accumulate) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -28,7 +31,7 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
     if (p >= 0) prow = pos_table + (size_t)min(p, max_positions - 1) * hidden;
   }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    out[i] = to_f<T>(row[i]) * scale + (prow ? to_f<T>(prow[i]) : 0.f);
+    out[i] = (accumulate ? out[i] : 0.f) + (to_f<T>(row[i]) * scale + (prow ? to_f<T>(prow[i]) : 0.f));
 }
 
 __global__ void scale_f32_kernel(float* x, size_t n, float scale) {
@@ -152,17 +155,24 @@ __global__ void add_residual_kernel(float* __restrict__ resid, const T* __restri
   if (i < n) resid[i] += to_f<T>(add[i]);
 }
 
-// out[r, i] = silu(gu[r, i]) * gu[r, inter + i]    (engine/ek_kernels.py:125-143)
+// out[r, i] = act(gu[r, i]) * gu[r, inter + i]    (silu: engine/ek_kernels.py:125-143)
 // VEC: inter is a multiple of 4; a thread handles four neighbours.  A 16-bit result takes the
 // fast exponential and division (a few 32-bit ulps, far below its own rounding); a 32-bit
 // result the exact ones.
-template <typename T>
+// ACT 0: silu(g) = g / (1 + exp(-g)).  ACT 1: the tanh form of GELU,
+// 0.5 g (1 + tanh(u)) with u = sqrt(2/pi) (g + 0.044715 g^3), which is g / (1 + exp(-2u)).
+template <typename T, int ACT = 0>
 __device__ __forceinline__ float silu_of(float g) {
+  if (ACT == 1) {
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    if (sizeof(T) == 2) return __fdividef(g, 1.f + __expf(-2.f * u));
+    return 0.5f * g * (1.f + tanhf(u));
+  }
   if (sizeof(T) == 2) return __fdividef(g, 1.f + __expf(-g));
   return g / (1.f + expf(-g));
 }
 
-template <typename T, bool VEC>
+template <typename T, bool VEC, int ACT>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter) {
   const size_t r = blockIdx.y;
   const T* g_row = gu + r * 2 * inter;
@@ -171,17 +181,18 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= inter) return;
     const float4 g = Vec4<T>::load(g_row + i), u = Vec4<T>::load(g_row + inter + i);
-    Vec4<T>::store(o_row + i, make_float4(silu_of<T>(g.x) * u.x, silu_of<T>(g.y) * u.y,
-                                          silu_of<T>(g.z) * u.z, silu_of<T>(g.w) * u.w));
+    Vec4<T>::store(o_row + i, make_float4(silu_of<T, ACT>(g.x) * u.x, silu_of<T, ACT>(g.y) * u.y,
+                                          silu_of<T, ACT>(g.z) * u.z, silu_of<T, ACT>(g.w) * u.w));
   } else {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
     const float g = to_f<T>(g_row[i]), u = to_f<T>(g_row[inter + i]);
-    o_row[i] = from_f<T>(silu_of<T>(g) * u);
+    o_row[i] = from_f<T>(silu_of<T, ACT>(g) * u);
   }
 }
 
 // The same for bfloat16 rows whose halves start on 16-byte boundaries: eight neighbours a thread.
+template <int ACT>
 __global__ void silu_mul_wide_kernel(bf16* __restrict__ out, const bf16* __restrict__ gu, int inter) {
   const size_t r = blockIdx.y;
   const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
@@ -195,7 +206,7 @@ __global__ void silu_mul_wide_kernel(bf16* __restrict__ out, const bf16* __restr
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float2 a = __bfloat1622float2(g2[j]), b = __bfloat1622float2(u2[j]);
-    __nv_bfloat162 h = __floats2bfloat162_rn(silu_of<bf16>(a.x) * b.x, silu_of<bf16>(a.y) * b.y);
+    __nv_bfloat162 h = __floats2bfloat162_rn(silu_of<bf16, ACT>(a.x) * b.x, silu_of<bf16, ACT>(a.y) * b.y);
     w[j] = *reinterpret_cast<uint32_t*>(&h);
   }
   *reinterpret_cast<uint4*>(out + r * inter + i) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -229,20 +240,20 @@ static int launch_rmsnorm(void* y, float* resid, const void* add, const float* g
                          (const T*)add, gain, rows, eps, hidden, write_back);
 }
 
-template <typename T>
+template <typename T, int ACT>
 static int launch_silu_mul(void* out, const void* gu, int rows, int inter, cudaStream_t stream) {
   if (rows <= 0 || inter <= 0) return 0;
   if (rows > 65535) return EK_ERR_ARG;
   if (sizeof(T) == 2 && inter % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)gu % 16) == 0) {
     dim3 wide((inter / 8 + 255) / 256, rows);
-    silu_mul_wide_kernel<<<wide, 256, 0, stream>>>((bf16*)out, (const bf16*)gu, inter);
+    silu_mul_wide_kernel<ACT><<<wide, 256, 0, stream>>>((bf16*)out, (const bf16*)gu, inter);
     EK_RETURN_LAUNCH_STATUS();
   }
   const bool vec = inter % 4 == 0 && ((uintptr_t)out % 8) == 0 && ((uintptr_t)gu % 8) == 0;
   const int per_thread = vec ? 4 : 1;
   dim3 grid((inter / per_thread + 255) / 256 + (inter % per_thread ? 1 : 0), rows);
-  if (vec) silu_mul_kernel<T, true><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);
-  else silu_mul_kernel<T, false><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);
+  if (vec) silu_mul_kernel<T, true, ACT><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);
+  else silu_mul_kernel<T, false, ACT><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -253,7 +264,8 @@ using namespace ek;
 #define EK_INSTANTIATE(SUFFIX, T)                                                               \
   EK_EXPORT int ek_embed_##SUFFIX(float* resid, const void* table, const int* ids, int n_tokens, \
                                   int hidden, int vocab, float scale, const void* pos_table,    \
-                                  const int* positions, int max_positions, cudaStream_t stream) { \
+                                  const int* positions, int max_positions, int accumulate,      \
+                                  cudaStream_t stream) {                                        \
     if (n_tokens <= 0) return 0;                                                                \
     if (pos_table && (!positions || max_positions <= 0)) return EK_ERR_ARG;                     \
     /* A plain launch, on purpose: the first kernel of a step starts only when everything   */ \
@@ -263,7 +275,7 @@ using namespace ek;
     embed_kernel<T><<<dim3(n_tokens), dim3(256), 0, stream>>>(resid, (const T*)table, ids,     \
                                                                hidden, vocab, scale,            \
                                                                (const T*)pos_table, positions,  \
-                                                               max_positions);                  \
+                                                               max_positions, accumulate);      \
     EK_RETURN_LAUNCH_STATUS();                                                                  \
   }                                                                                             \
   EK_EXPORT int ek_rmsnorm_##SUFFIX(void* y, float* resid, const void* add, const float* gain,  \
@@ -280,7 +292,14 @@ using namespace ek;
   }                                                                                             \
   EK_EXPORT int ek_silu_mul_##SUFFIX(void* out, const void* gu, int rows, int inter,            \
                                      cudaStream_t stream) {                                     \
-    return launch_silu_mul<T>(out, gu, rows, inter, stream);                                    \
+    return launch_silu_mul<T, 0>(out, gu, rows, inter, stream);                                 \
+  }                                                                                             \
+  /* act 0: silu, 1: gelu (tanh form) */                                                        \
+  EK_EXPORT int ek_act_mul_##SUFFIX(void* out, const void* gu, int rows, int inter, int act,    \
+                                    cudaStream_t stream) {                                      \
+    if (act == 0) return launch_silu_mul<T, 0>(out, gu, rows, inter, stream);                   \
+    if (act == 1) return launch_silu_mul<T, 1>(out, gu, rows, inter, stream);                   \
+    return EK_ERR_ARG;                                                                          \
   }
 
 EK_INSTANTIATE(f32, float)

@@ -13,6 +13,21 @@ namespace ek {
 
 constexpr int kRopeWarps = 4;
 
+// What a design may ask for beyond norm and rotation (all off in a zeroed struct):
+// biases of the projections, added here in 32-bit before anything else ([heads * head size] each);
+// a query temperature, q *= 1 + coef * ln(floor((position + 1) / every) + 1), which sharpens the
+// scores of late positions step by step; and values that are the keys as projected (bias added,
+// before the key norm and rotation): the row then has no value heads, and a key head is stored
+// twice, raw in the value pages and normalised in the key pages.
+struct QkExtras {
+  const float* q_bias;
+  const float* k_bias;
+  const float* v_bias;
+  float q_temp_coef;
+  int q_temp_every;
+  int v_from_k;
+};
+
 
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
@@ -22,7 +37,7 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
                                        const float* __restrict__ sin_tab, int rot_dim,
                                        const int* positions, const int* token_slot,
                                        PagedKV cache,
-                                       int n_q_heads, float eps, int write_kv) {
+                                       int n_q_heads, float eps, int write_kv, QkExtras ex) {
   __shared__ __align__(16) float buf[kRopeWarps][EK_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
@@ -30,7 +45,7 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * kRopeWarps + warp;
   const int n_kv = cache.heads, d = cache.head_dim;
-  if (head >= n_q_heads + 2 * n_kv) return;
+  if (head >= n_q_heads + (ex.v_from_k ? 1 : 2) * n_kv) return;
   const int pos = positions[t];
   if (pos < 0) return;                        // a row of a finished sequence
   const bool is_q = head < n_q_heads;
@@ -39,21 +54,29 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
 
   T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
   T* dst = src;
+  T* dst_raw = nullptr;                       // where a key head also goes as the value
+  const float* bias = is_q ? ex.q_bias : (is_k ? ex.k_bias : ex.v_bias);
+  if (bias) bias += (size_t)(is_q ? head : (is_k ? head - n_q_heads : head - n_q_heads - n_kv)) * d;
   if (!is_q) {
     const int slot = token_slot[t];
     const int page = cache.block_table[(size_t)slot * cache.table_stride + pos / EK_PAGE];
     const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv;
     dst = (T*)(is_k ? cache.k : cache.v) + page_offset(cache, page, kv_head, pos);
+    if (is_k && ex.v_from_k) dst_raw = (T*)cache.v + page_offset(cache, page, kv_head, pos);
   }
 
   // Four neighbouring dimensions a lane when the sizes allow (head size a multiple of 4 and
   // the rotated half a multiple of 4), else one.
   const bool vec = (d % 4 == 0) && (rot_dim % 8 == 0) && (row_stride % 4 == 0);
-  if (!is_q && !is_k) {                       // values: a copy
+  if (!is_q && !is_k) {                       // values: a copy (plus the bias)
     if (vec) {
-      for (int i = lane * 4; i < d; i += 128) Vec4<T>::store(dst + i, Vec4<T>::load(src + i));
+      for (int i = lane * 4; i < d; i += 128) {
+        float4 v = Vec4<T>::load(src + i);
+        if (bias) { v.x += bias[i]; v.y += bias[i + 1]; v.z += bias[i + 2]; v.w += bias[i + 3]; }
+        Vec4<T>::store(dst + i, v);
+      }
     } else {
-      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+      for (int i = lane; i < d; i += 32) dst[i] = bias ? from_f<T>(to_f<T>(src[i]) + bias[i]) : src[i];
     }
     return;
   }
@@ -62,13 +85,17 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
   float ss = 0.f;
   if (vec) {
     for (int i = lane * 4; i < d; i += 128) {
-      const float4 v = Vec4<T>::load(src + i);
+      float4 v = Vec4<T>::load(src + i);
+      if (bias) { v.x += bias[i]; v.y += bias[i + 1]; v.z += bias[i + 2]; v.w += bias[i + 3]; }
+      if (dst_raw) Vec4<T>::store(dst_raw + i, v);
       *reinterpret_cast<float4*>(&buf[warp][i]) = v;
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   } else {
     for (int i = lane; i < d; i += 32) {
-      const float v = to_f<T>(src[i]);
+      float v = to_f<T>(src[i]);
+      if (bias) v += bias[i];
+      if (dst_raw) dst_raw[i] = from_f<T>(v);
       buf[warp][i] = v;
       ss += v * v;
     }
@@ -78,6 +105,8 @@ __global__ void qk_norm_rope_kv_kernel(T* qkv, int row_stride,
     ss = warp_sum(ss);
     rstd = rsqrtf(ss / (float)d + eps);
   }
+  if (is_q && ex.q_temp_coef != 0.f)          // the rotation is linear: the factor may come first
+    rstd *= 1.f + ex.q_temp_coef * logf((float)((pos + 1) / ex.q_temp_every) + 1.f);
   __syncwarp();
   const int half = rot_dim >> 1;
   const float* cs = cos_tab + (size_t)pos * half;
@@ -286,13 +315,14 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
                   const float* cos_tab, const float* sin_tab, int rot_dim, const int* positions,
                   const int* token_slot, void* k_pages, void* v_pages, const int* block_table,
                   int table_stride, int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
-                  float eps, int write_kv, cudaStream_t stream) {
+                  float eps, int write_kv, QkExtras ex, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || (head_dim & 1) || rot_dim < 0 ||
-      rot_dim > head_dim || (rot_dim & 1) || n_tokens > 2147483647 / 2)
+  if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || rot_dim < 0 || rot_dim > head_dim ||
+      (rot_dim & 1) || n_tokens > 2147483647 / 2 || (ex.q_temp_coef != 0.f && ex.q_temp_every <= 0))
     return EK_ERR_ARG;
   PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};
-  if (wide_takes<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, k_pages, v_pages,
+  const bool plain = !ex.q_bias && !ex.k_bias && !ex.v_bias && ex.q_temp_coef == 0.f && !ex.v_from_k;
+  if (plain && wide_takes<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, k_pages, v_pages,
                     n_tokens, head_dim)) {
     bf16* rows = (bf16*)qkv;
     if (head_dim == 64)
@@ -304,11 +334,11 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
     return launch_wide<256>(rows, row_stride, q_gain, k_gain, cos_tab, sin_tab, positions, token_slot,
                             cache, n_tokens, n_q_heads, eps, write_kv, stream);
   }
-  const int heads = n_q_heads + 2 * n_kv_heads;
+  const int heads = n_q_heads + (ex.v_from_k ? 1 : 2) * n_kv_heads;
   dim3 grid(n_tokens, (heads + kRopeWarps - 1) / kRopeWarps);
   return (int)launch_pdl(qk_norm_rope_kv_kernel<T>, grid, dim3(kRopeWarps * 32), 0, stream, (T*)qkv,
                          row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions,
-                         token_slot, cache, n_q_heads, eps, write_kv);
+                         token_slot, cache, n_q_heads, eps, write_kv, ex);
 }
 
 }  // namespace ek
@@ -322,7 +352,23 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
       cudaStream_t stream) {                                                                   \
     return ek::launch<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, \
                          token_slot, k_pages, v_pages, block_table, table_stride, n_tokens,    \
-                         n_q_heads, n_kv_heads, head_dim, eps, write_kv, stream);              \
+                         n_q_heads, n_kv_heads, head_dim, eps, write_kv, ek::QkExtras{},       \
+                         stream);                                                              \
+  }                                                                                            \
+  /* The same with the options of ek::QkExtras: biases (32-bit, nullable), the query         */ \
+  /* temperature (coef 0: none) and values taken from the keys as projected (the rows then   */ \
+  /* hold (NQ + NKV) heads).                                                                  */ \
+  EK_EXPORT int ek_qk_prepare_kv_##SUFFIX(                                                      \
+      void* qkv, int row_stride, const float* q_gain, const float* k_gain, const float* cos_tab, \
+      const float* sin_tab, int rot_dim, const int* positions, const int* token_slot,          \
+      void* k_pages, void* v_pages, const int* block_table, int table_stride, int n_tokens,    \
+      int n_q_heads, int n_kv_heads, int head_dim, float eps, int write_kv,                    \
+      const float* q_bias, const float* k_bias, const float* v_bias, float q_temp_coef,        \
+      int q_temp_every, int v_from_k, cudaStream_t stream) {                                   \
+    ek::QkExtras ex{q_bias, k_bias, v_bias, q_temp_coef, q_temp_every, v_from_k};              \
+    return ek::launch<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, positions, \
+                         token_slot, k_pages, v_pages, block_table, table_stride, n_tokens,    \
+                         n_q_heads, n_kv_heads, head_dim, eps, write_kv, ex, stream);          \
   }
 
 EK_INSTANTIATE(f32, float)

@@ -38,6 +38,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
         out[ts.name] = ts
     for layer in spec.layers:
         for role in _LAYER_ROLES:
+            if getattr(layer, role) is None:         # a layer without a feed-forward
+                continue
             for ts in _part_tensors(role, getattr(layer, role)):
                 out[ts.name] = ts
         for norm in layer.norms.values():
@@ -48,7 +50,7 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
 
 def ignorable_tensors(spec: ModelSpec) -> List[str]:
     """Names a checkpoint may hold although the model does not read them."""
-    return [spec.lm_head.name] if spec.lm_head.optional_alias is not None else []
+    return ([spec.lm_head.name] if spec.lm_head.optional_alias is not None else []) + list(spec.ignorable)
 
 
 class DecoderModel:
@@ -60,7 +62,8 @@ class DecoderModel:
         self.blocks = []
         for layer in spec.layers:
             mixer = lookup_part("mixer", layer.mixer.kind)(layer.mixer, dtype, device)
-            ff = lookup_part("feed_forward", layer.feed_forward.kind)(layer.feed_forward, dtype, device)
+            ff = None if layer.feed_forward is None else \
+                lookup_part("feed_forward", layer.feed_forward.kind)(layer.feed_forward, dtype, device)
             block_cls = lookup_part("block", layer.block.kind)
             missing = [n for n in block_cls.norm_names(layer.block) if n not in layer.norms]
             if missing:
@@ -85,7 +88,8 @@ class DecoderModel:
         self.final_norm.load(tensors)
         for block in self.blocks:
             block.mixer.load(tensors)
-            block.feed_forward.load(tensors)
+            if block.feed_forward is not None:
+                block.feed_forward.load(tensors)
             for norm in block.norms.values():
                 norm.load(tensors)
 
@@ -120,7 +124,8 @@ class DecoderModel:
         for run in self.spec.schedule:
             b = self.blocks[run.layer]
             for part in (b.mixer, b.feed_forward, *b.norms.values()):
-                total += part.bytes_read_per_step(n_tokens)
+                if part is not None:
+                    total += part.bytes_read_per_step(n_tokens)
         return total
 
     # -- one step -----------------------------------------------------------------
@@ -137,11 +142,18 @@ class DecoderModel:
         schedule = self.spec.schedule
         for i, run in enumerate(schedule):
             block = self.blocks[run.layer]
+            if run.add_embedding:
+                # a further pass over a stretch of layers starts: the embedding output joins the
+                # stream again (the pending output of the block before is added by the next norm)
+                kernels.embed(stream, self.embedding, ctx.token_ids, t, scale=self.spec.embedding_multiplier,
+                              pos_table=self.position_table, positions=ctx.positions, accumulate=True)
             entry = cache.entry(run.cache) if run.cache is not None and \
                 block.mixer.cache_spec() is not None else None
             # a block that can leave its last add and the next norm to its own last product is told
             # which norm comes next (none after the last block: the final norm picks rows)
-            follower = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            # (and none when the embedding output is added in between: the norm would miss it)
+            follower = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) and \
+                not schedule[i + 1].add_embedding else None
             next_norm = getattr(follower, "first_norm", lambda: None)() if follower is not None else None
             if next_norm is not None:
                 pending = block.forward(stream, pending, ctx, entry, run.writes_cache, next_norm=next_norm)

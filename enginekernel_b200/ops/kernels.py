@@ -88,18 +88,20 @@ def _per_dtype(module, name, argtypes):
 
 
 # ------------------------------------------------------------------ elementwise
-_embed = _per_dtype("elementwise", "ek_embed", [_P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, c_int, _P])
+_embed = _per_dtype("elementwise", "ek_embed", [_P, _P, _P, c_int, c_int, c_int, c_float, _P, _P, c_int, c_int, _P])
 _scale_f32 = Function("elementwise", "ek_scale_f32", [_P, c_longlong, c_float, _P])
 _rmsnorm = _per_dtype("elementwise", "ek_rmsnorm",
                       [_P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, _P])
 _add_residual = _per_dtype("elementwise", "ek_add_residual", [_P, _P, c_longlong, _P])
-_silu_mul = _per_dtype("elementwise", "ek_silu_mul", [_P, _P, c_int, c_int, _P])
+_act_mul = _per_dtype("elementwise", "ek_act_mul", [_P, _P, c_int, c_int, c_int, _P])
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 
-def embed(resid, table, ids, n_tokens, scale=1.0, pos_table=None, positions=None):
+def embed(resid, table, ids, n_tokens, scale=1.0, pos_table=None, positions=None, accumulate=False):
     """resid[t, :] = table[ids[t], :] * scale as 32-bit, for the first ``n_tokens`` ids; with
     ``pos_table`` [positions, hidden] also + pos_table[positions[t], :] (rows whose position is
-    negative get none).  A plain launch: the first kernel of a step."""
+    negative get none).  A plain launch: the first kernel of a step.  ``accumulate``: the same
+    values are added to what ``resid`` holds instead (the embedding output fed in again)."""
     _need_cuda(resid, table, ids, pos_table, positions)
     _need(resid.dtype == torch.float32 and ids.dtype == torch.int32, "embed: resid f32, ids int32")
     _need(table.is_contiguous() and resid.is_contiguous(), "embed: contiguous tensors")
@@ -112,9 +114,10 @@ def embed(resid, table, ids, n_tokens, scale=1.0, pos_table=None, positions=None
               "embed: position table [positions, hidden] in the embedding's dtype, int32 positions")
         max_positions = pos_table.shape[0]
     if lib.recording():
-        lib.annotate(bytes=n_tokens * hidden * (table.element_size() * (2 if pos_table is not None else 1) + 4))
+        lib.annotate(bytes=n_tokens * hidden * (table.element_size() * (2 if pos_table is not None else 1)
+                                                + (8 if accumulate else 4)))
     _embed[table.dtype](_ptr(resid), _ptr(table), _ptr(ids), n_tokens, hidden, vocab, float(scale),
-                        _ptr(pos_table), _ptr(positions), max_positions, _stream())
+                        _ptr(pos_table), _ptr(positions), max_positions, 1 if accumulate else 0, _stream())
 
 
 def scale_(x, scale, n=None):
@@ -156,17 +159,25 @@ def add_residual(resid, x, n_rows=None):
 
 def silu_mul(out, gu, n_rows=None):
     """out[r, i] = silu(gu[r, i]) * gu[r, I + i] for gu of width 2I."""
+    act_mul(out, gu, "silu", n_rows)
+
+
+def act_mul(out, gu, activation="silu", n_rows=None):
+    """out[r, i] = act(gu[r, i]) * gu[r, I + i] for gu of width 2I; ``activation`` is ``"silu"`` or
+    ``"gelu_tanh"`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
     _need_cuda(out, gu)
+    _need(activation in GATE_ACTIVATIONS, f"act_mul: no activation {activation!r}")
     inter = gu.shape[-1] // 2
     _need(gu.shape[-1] == 2 * inter and out.shape[-1] == inter and out.dtype == gu.dtype,
-          "silu_mul: out must be [rows, I] for gu [rows, 2I]")
-    _need(out.is_contiguous() and gu.is_contiguous(), "silu_mul: contiguous tensors")
+          "act_mul: out must be [rows, I] for gu [rows, 2I]")
+    _need(out.is_contiguous() and gu.is_contiguous(), "act_mul: contiguous tensors")
     rows = n_rows if n_rows is not None else gu.shape[0]
     if lib.recording():
         lib.annotate(bytes=3 * rows * inter * gu.element_size())
     for r0 in range(0, rows, 65535):
         r1 = min(rows, r0 + 65535)
-        _silu_mul[gu.dtype](_ptr(out[r0:]), _ptr(gu[r0:]), r1 - r0, inter, _stream())
+        _act_mul[gu.dtype](_ptr(out[r0:]), _ptr(gu[r0:]), r1 - r0, inter, GATE_ACTIVATIONS[activation],
+                           _stream())
 
 
 # ------------------------------------------------------------------ rope + cache write
@@ -176,9 +187,49 @@ _rope_kv = _per_dtype("rope_kv", "ek_qk_norm_rope_kv",
 
 
 def check_head_dim(head_dim):
-    if head_dim % 16 or not 16 <= head_dim <= MAX_HEAD_DIM:
+    if not 1 <= head_dim <= MAX_HEAD_DIM:
         raise KernelError(f"head size {head_dim} is not supported: the attention kernels take "
-                          f"multiples of 16 from 16 to {MAX_HEAD_DIM}")
+                          f"head sizes up to {MAX_HEAD_DIM}")
+
+
+_qk_prepare = _per_dtype("rope_kv", "ek_qk_prepare_kv",
+                         [_P, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int,
+                          c_int, c_int, c_float, c_int, _P, _P, _P, c_float, c_int, c_int, _P])
+
+
+def qk_prepare_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions, token_slot,
+                  k_pages, v_pages, block_table, n_q_heads, n_kv_heads, head_dim, eps,
+                  write_kv=True, q_bias=None, k_bias=None, v_bias=None, q_temperature=None,
+                  values_from_keys=False):
+    """:func:`qk_norm_rope_kv` with what some designs put around it.  ``q_bias``, ``k_bias``,
+    ``v_bias`` (32-bit, [heads * D]) are added to the projections first; ``q_temperature=(coef,
+    every)`` multiplies the finished query by 1 + coef * ln(floor((position + 1) / every) + 1);
+    ``values_from_keys``: ``qkv`` is [T, (NQ + NKV) D] without value heads, and the value stored
+    for a token is its key as projected (bias added, before the key norm and rotation)."""
+    _need_cuda(qkv, cos, sin, positions, token_slot, k_pages, v_pages, block_table, q_bias, k_bias, v_bias)
+    check_head_dim(head_dim)
+    heads = n_q_heads + (1 if values_from_keys else 2) * n_kv_heads
+    _need(qkv.stride(-1) == 1 and qkv.shape[-1] == heads * head_dim, "qk_prepare_kv: qkv width")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+          and cos.shape[-1] * 2 == rot_dim, "qk_prepare_kv: 32-bit tables of rot_dim/2 columns")
+    _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype, "qk_prepare_kv: cache dtype")
+    _need(block_table.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32, "qk_prepare_kv: int32 indices")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.dtype == torch.float32 and g.numel() == head_dim), "qk gains: 32-bit [D]")
+    for b, n in ((q_bias, n_q_heads), (k_bias, n_kv_heads), (v_bias, n_kv_heads)):
+        _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == n * head_dim),
+              "qk_prepare_kv: biases are 32-bit [heads * D]")
+    _need(not (values_from_keys and v_bias is not None), "qk_prepare_kv: values taken from keys have no bias")
+    coef, every = (0.0, 1) if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+    _need(every >= 1, "qk_prepare_kv: the temperature's step must be at least one position")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * head_dim * qkv.element_size() * (2 * n_q_heads + 3 * n_kv_heads))
+    _qk_prepare[qkv.dtype](_ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), _ptr(cos), _ptr(sin),
+                           rot_dim, _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
+                           _ptr(block_table), block_table.stride(0), n_tokens, n_q_heads, n_kv_heads,
+                           head_dim, float(eps), 1 if write_kv else 0, _ptr(q_bias), _ptr(k_bias),
+                           _ptr(v_bias), coef, every, 1 if values_from_keys else 0, _stream())
 
 
 def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions, token_slot,
@@ -207,13 +258,21 @@ def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions,
 # ------------------------------------------------------------------ attention
 _attn_generic = _per_dtype("attention_generic", "ek_attention_generic",
                            [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_int, _P, _P, _P])
+                            c_float, c_int, c_int, c_int, _P, _P, c_float, _P])
+_NO_SINK = float("-inf")
+
+
+def _sink(sink) -> float:
+    """The kernels' encoding of an attention sink: its score, or -inf for none."""
+    return _NO_SINK if sink is None else float(sink)
 
 
 def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
                       n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
-                      keys_per_split=0, part_acc=None, part_ml=None):
-    """out[t, h*D:(h+1)*D] = softmax(scale q.K^T) V over the keys token t may see.
+                      keys_per_split=0, part_acc=None, part_ml=None, sink=None):
+    """out[t, h*D:(h+1)*D] = softmax(scale q.K^T) V over the keys token t may see.  ``sink``: the
+    score of one more key without a value that every query sees - exp(sink) is added to the
+    softmax denominator (the same in every attention kernel below).
 
     ``q`` is any tensor whose row t starts with the NQ*D query values (the fused q/k/v
     rows qualify).  With ``n_splits`` > 1 the keys are cut every ``keys_per_split`` and
@@ -233,14 +292,14 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
                            _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                            n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
                            int(window or 0), n_splits, keys_per_split, _ptr(part_acc),
-                           _ptr(part_ml), _stream())
+                           _ptr(part_ml), _sink(sink), _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
 
 
 _attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16",
                              [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_int, c_int, c_int, _P, _P, _P])
+                              c_float, c_int, c_int, c_int, _P, _P, c_float, _P])
 
 
 def attention_decode_supported(dtype, head_dim):
@@ -249,7 +308,7 @@ def attention_decode_supported(dtype, head_dim):
 
 def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
                           n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
-                          keys_per_split=0, part_acc=None, part_ml=None):
+                          keys_per_split=0, part_acc=None, part_ml=None, sink=None):
     """One query token per row of ``q`` (bfloat16, head_dim a multiple of 32): same contract
     as :func:`attention_generic`; ``keys_per_split`` must be a multiple of 16, or 0 to cut
     every token's own visible keys into ``n_splits`` equal parts."""
@@ -268,14 +327,14 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
     _attn_decode_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                       _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                       n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
-                      n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _stream())
+                      n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _sink(sink), _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
 
 
 _attn_decode_tma = Function("attention_decode_tma", "ek_attention_decode_tma",
                             [_P, _P, c_int, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int,
-                             c_float, c_int, c_int, _P, _P])
+                             c_float, c_int, c_int, _P, c_float, _P])
 _attn_decode_tma_max = Function("attention_decode_tma", "ek_attention_decode_tma_max_splits", [c_int],
                                 check_status=False)
 DECODE_TMA_PORTABLE_SPLITS = 8
@@ -298,7 +357,7 @@ def attention_decode_tma_supported(dtype, head_dim, n_q_heads, n_kv_heads):
 
 
 def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
-                         n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1):
+                         n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1, sink=None):
     """One new token per sequence (bfloat16, head size 64 or 128, at most 16 heads a group): the
     cache pages come by TMA, started before the kernel ahead has finished; ``n_splits`` (1 to 8)
     blocks (16 where :func:`decode_tma_max_splits` says so) share a token's pages and merge inside
@@ -324,12 +383,12 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
     _attn_decode_tma(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                      _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                      block_table.stride(0), n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
-                     int(window or 0), n_splits, _ptr(tc_status(q.device)), _stream())
+                     int(window or 0), n_splits, _ptr(tc_status(q.device)), _sink(sink), _stream())
 
 
 _attn_prefill_bf16 = Function("attention_prefill_bf16", "ek_attention_prefill_bf16",
                               [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int,
-                               c_int, c_int, c_float, c_int, _P])
+                               c_int, c_int, c_float, c_int, c_float, _P])
 
 
 def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
@@ -339,7 +398,7 @@ def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
 
 def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
                            v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale,
-                           window=None):
+                           window=None, sink=None):
     """Several new tokens per sequence (bfloat16): sequence b owns rows cu_seqlens[b] ..
     cu_seqlens[b+1] of ``q``, which stand at consecutive positions; their keys and values
     are already in the pages."""
@@ -354,12 +413,12 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
     _attn_prefill_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                        _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
                        _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, head_dim,
-                       float(scale), int(window or 0), _stream())
+                       float(scale), int(window or 0), _sink(sink), _stream())
 
 
 _attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",
                             [_P, _P, c_int, _P, c_int, c_int, _P, _P, c_int, _P, c_int, c_int,
-                             c_int, c_int, c_float, c_int, _P, _P])
+                             c_int, c_int, c_float, c_int, _P, c_float, _P])
 _attn_prefill_tiles = Function("attention_prefill_tc", "ek_attention_prefill_tiles",
                                [_P, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
 PREFILL_TC_ROWS = 128       # (token, query head of a group) rows a block of attention_prefill_tc owns
@@ -409,7 +468,7 @@ def attention_prefill_tiles(tiles, n_tokens, positions, token_slot, cu_seqlens, 
 
 def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
                          v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale, window=None,
-                         tiles=None, n_tiles=0):
+                         tiles=None, n_tiles=0, sink=None):
     """:func:`attention_prefill_bf16` on tcgen05 tensor cores (head sizes 64 and 128, groups
     that divide 128): TMA-fed pages, scores and P.V in TMEM.  ``tiles`` / ``n_tiles``: the table
     :func:`attention_prefill_tiles` made for this step (made once, before the step's first
@@ -436,7 +495,7 @@ def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_
     _attn_prefill_tc(_ptr(out), _ptr(q), q.stride(0), _ptr(tiles), n_tiles, n_tokens, _ptr(k_pages),
                      _ptr(v_pages), k_pages.shape[0], _ptr(block_table), block_table.stride(0), n_q_heads,
                      n_kv_heads, head_dim, float(scale), int(window or 0),
-                     _ptr(tc_status(q.device)), _stream())
+                     _ptr(tc_status(q.device)), _sink(sink), _stream())
 
 
 # ------------------------------------------------------------------ matrix products

@@ -12,6 +12,17 @@ Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``sc
 position PartSpec or None).  Tensors: ``q`` [NH*D, H], ``k``, ``v`` [NKV*D, H], ``o``
 [H, NH*D], and with q/k norm ``q_norm``, ``k_norm`` [D].  q, k and v are concatenated at
 load as the reference does (engine/ek_model.py:140-144).
+
+Optional parameters, all off by default, for designs that differ there:
+
+``bias``               which of ``"q"``, ``"k"``, ``"v"`` carry a bias (tensors ``q_bias`` ...
+                       [heads * D]); it is added in 32-bit before the head norm.
+``values``             ``"keys"``: there is no value projection - a token's value is its key as
+                       projected (with bias, before the key's norm and rotation).
+``query_temperature``  ``(coef, every)``: the query of the token at position p is multiplied by
+                       1 + coef * ln(floor((p + 1) / every) + 1).
+``sink``               the score of one more key without a value that every query sees: its
+                       exponential is one more term of the softmax denominator (0.0: "+ 1").
 """
 
 from __future__ import annotations
@@ -34,10 +45,14 @@ class Attention(Mixer):
     def tensors(cls, spec):
         p, w = spec.params, spec.weights
         h, nh, nkv, d = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"]
-        out = [TensorSpec(w["q"], (nh * d, h)), TensorSpec(w["k"], (nkv * d, h)),
-               TensorSpec(w["v"], (nkv * d, h)), TensorSpec(w["o"], (h, nh * d))]
+        out = [TensorSpec(w["q"], (nh * d, h)), TensorSpec(w["k"], (nkv * d, h))]
+        if p.get("values", "projection") != "keys":
+            out.append(TensorSpec(w["v"], (nkv * d, h)))
+        out.append(TensorSpec(w["o"], (h, nh * d)))
         if p.get("qk_norm_eps") is not None:
             out += [TensorSpec(w["q_norm"], (d,), "gain"), TensorSpec(w["k_norm"], (d,), "gain")]
+        for which in p.get("bias") or ():
+            out.append(TensorSpec(w[which + "_bias"], ((nh if which == "q" else nkv) * d,)))
         return out
 
     def __init__(self, spec, dtype, device):
@@ -49,6 +64,17 @@ class Attention(Mixer):
         self.scale = float(self.param("scale"))
         self.qk_norm_eps = spec.params.get("qk_norm_eps")
         self.window = spec.params.get("window")
+        self.biased = tuple(spec.params.get("bias") or ())
+        self.values_from_keys = spec.params.get("values", "projection") == "keys"
+        self.query_temperature = spec.params.get("query_temperature")
+        self.sink = spec.params.get("sink")
+        if spec.params.get("values", "projection") not in ("projection", "keys"):
+            raise ValueError("attention: values are 'projection' or 'keys'")
+        if any(b not in ("q", "k", "v") for b in self.biased) or (self.values_from_keys and "v" in self.biased):
+            raise ValueError("attention: bias names q, k, v (v only with a value projection)")
+        if self.query_temperature is not None and int(self.query_temperature[1]) < 1:
+            raise ValueError("attention: the query temperature steps every >= 1 positions")
+        self.bias = {"q": None, "k": None, "v": None}
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         kernels.check_head_dim(self.head_dim)
@@ -68,8 +94,9 @@ class Attention(Mixer):
 
     def begin_step(self, ctx):
         """The table of tiles of the tcgen05 prompt attention, once per step and shape of the heads."""
-        if ctx.is_decode or ctx.n_seqs > kernels.PREFILL_TC_MAX_SEQS or not kernels.attention_prefill_tc_supported(
-                self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
+        if ctx.is_decode or ctx.n_seqs > kernels.PREFILL_TC_MAX_SEQS or not self.scale > 0 or \
+                not kernels.attention_prefill_tc_supported(self.dtype, self.head_dim, self.num_heads,
+                                                           self.num_kv_heads):
             return
         key = self._tiles_key()
         if key in ctx.shared:
@@ -83,16 +110,18 @@ class Attention(Mixer):
 
     def load(self, tensors):
         w = self.spec.weights
-        self.w_qkv = torch.cat([tensors[w["q"]], tensors[w["k"]], tensors[w["v"]]], dim=0) \
-            .to(self.dtype).contiguous()
+        rows = [tensors[w["q"]], tensors[w["k"]]] + ([] if self.values_from_keys else [tensors[w["v"]]])
+        self.w_qkv = torch.cat(rows, dim=0).to(self.dtype).contiguous()
+        for which in self.biased:
+            self.bias[which] = tensors[w[which + "_bias"]].to(torch.float32).contiguous()
         self.w_o = tensors[w["o"]].to(self.dtype).contiguous()
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[w["q_norm"]].to(torch.float32).contiguous()
             self.k_gain = tensors[w["k_norm"]].to(torch.float32).contiguous()
 
     def bytes_read_per_step(self, n_tokens):
-        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o, self.q_gain, self.k_gain)
-                   if t is not None)
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o, self.q_gain, self.k_gain,
+                                                          *self.bias.values()) if t is not None)
 
     # ------------------------------------------------------------------
     takes_deferred_norm = True
@@ -125,26 +154,38 @@ class Attention(Mixer):
             self._attend(out, qkv, ctx, entry)
             return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
         qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
-        kernels.qk_norm_rope_kv(
-            qkv, t, self.q_gain, self.k_gain,
-            pos.cos if pos else _no_table(self.device), pos.sin if pos else _no_table(self.device),
-            pos.rotary_dim if pos else 0, ctx.positions, ctx.token_slot, entry.k_pages,
-            entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim,
-            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_kv=writes_cache)
+        prepare = (qkv, t, self.q_gain, self.k_gain,
+                   pos.cos if pos else _no_table(self.device), pos.sin if pos else _no_table(self.device),
+                   pos.rotary_dim if pos else 0, ctx.positions, ctx.token_slot, entry.k_pages,
+                   entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim,
+                   self.qk_norm_eps if self.qk_norm_eps is not None else 0.0)
+        if self._plain:
+            kernels.qk_norm_rope_kv(*prepare, write_kv=writes_cache)
+        else:
+            kernels.qk_prepare_kv(*prepare, write_kv=writes_cache, q_bias=self.bias["q"],
+                                  k_bias=self.bias["k"], v_bias=self.bias["v"],
+                                  q_temperature=self.query_temperature,
+                                  values_from_keys=self.values_from_keys)
         out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
         self._attend(out, qkv, ctx, entry)
         return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
 
+    @property
+    def _plain(self):
+        """None of the optional parameters that change what happens between the projection and
+        the cache is on (the sink only changes the softmax)."""
+        return not self.biased and not self.values_from_keys and self.query_temperature is None
+
     def _fuses_rope(self, x, ctx):
         xin = x.scaled if isinstance(x, DeferredNorm) else x
         pos = self.position
-        return (self.dtype == torch.bfloat16 and ctx.n_tokens <= FUSE_ROPE_ROWS
+        return (self._plain and self.dtype == torch.bfloat16 and ctx.n_tokens <= FUSE_ROPE_ROWS
                 and self.head_dim == kernels.QKV_ROPE_HEAD_DIM and pos is not None
                 and getattr(pos, "rotary_dim", 0) == self.head_dim and tc_takes(xin, self.w_qkv))
 
     def _fuses_rope_of_many_rows(self, x, ctx):
         pos = self.position
-        if (isinstance(x, DeferredNorm) or self.dtype != torch.bfloat16
+        if (not self._plain or isinstance(x, DeferredNorm) or self.dtype != torch.bfloat16
                 or self.head_dim != kernels.QKV_ROPE_HEAD_DIM or pos is None
                 or getattr(pos, "rotary_dim", 0) != self.head_dim):
             return False
@@ -158,8 +199,9 @@ class Attention(Mixer):
         if not ctx.is_decode and kernels.attention_prefill_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
             prefill = kernels.attention_prefill_bf16
-            if ctx.n_seqs <= kernels.PREFILL_TC_MAX_SEQS and kernels.attention_prefill_tc_supported(
-                    self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
+            if ctx.n_seqs <= kernels.PREFILL_TC_MAX_SEQS and self.scale > 0 and \
+                    kernels.attention_prefill_tc_supported(self.dtype, self.head_dim, self.num_heads,
+                                                           self.num_kv_heads):
                 prefill = kernels.attention_prefill_tc      # tcgen05: head sizes 64 and 128
             extra = {}
             if prefill is kernels.attention_prefill_tc:
@@ -169,7 +211,7 @@ class Attention(Mixer):
             prefill(
                 out, qkv, t, ctx.positions, ctx.token_slot, ctx.cu_seqlens, ctx.n_seqs,
                 entry.k_pages, entry.v_pages, entry.block_table, self.num_heads, self.num_kv_heads,
-                self.head_dim, self.scale, self.window, **extra)
+                self.head_dim, self.scale, self.window, sink=self.sink, **extra)
             return
         if ctx.is_decode and t <= 65535 and kernels.attention_decode_tma_supported(
                 self.dtype, self.head_dim, self.num_heads, self.num_kv_heads):
@@ -185,7 +227,7 @@ class Attention(Mixer):
             kernels.attention_decode_tma(
                 out, qkv, t, ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages,
                 entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                self.window, splits)
+                self.window, splits, sink=self.sink)
             return
         if fast_decode:
             # blocks = tokens x KV heads (x 16-row blocks of the group); three fit an SM.  Split
@@ -216,7 +258,7 @@ class Attention(Mixer):
                 entry.block_table, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
                 self.window, splits, per_split, acc, ml)
         fn = kernels.attention_decode_bf16 if fast_decode else kernels.attention_generic
-        fn(*args)
+        fn(*args, sink=self.sink)
 
 
 _EMPTY = {}

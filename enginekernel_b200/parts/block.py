@@ -1,4 +1,5 @@
 """Pre-norm residual block: stream += mixer(norm(stream)); stream += ff(norm(stream)).
+A layer without a feed-forward is the first half alone (and needs only ``pre_mixer``).
 
 The add of a part's output is folded into the norm that follows it, so a block takes the
 previous block's not-yet-added output (``pending``) and returns its own
@@ -15,7 +16,12 @@ from .base import Block, DeferredNorm
 class PreNormBlock(Block):
     @classmethod
     def norm_names(cls, spec):
-        return ["pre_mixer", "pre_feed_forward"]
+        return ["pre_mixer"]             # and "pre_feed_forward" when there is a feed-forward
+
+    def __init__(self, spec, dtype, device, mixer, feed_forward, norms):
+        super().__init__(spec, dtype, device, mixer, feed_forward, norms)
+        if feed_forward is not None and "pre_feed_forward" not in norms:
+            raise ValueError("block 'pre_norm' needs the norm 'pre_feed_forward' before its feed-forward")
 
     def first_norm(self):
         """The norm that takes this block's incoming ``pending``, if the part behind it can read
@@ -29,6 +35,11 @@ class PreNormBlock(Block):
             a = pending                          # made for pre_mixer by the block before
         else:
             a = self.norms["pre_mixer"].forward(stream, ctx, add=pending)
+        if self.feed_forward is None:
+            # the mixer's output is this block's pending; the block behind may take it deferred
+            if self.mixer.defers_norm and next_norm is not None:
+                return self.mixer.forward(a, ctx, entry, writes_cache, defer=(stream, next_norm))
+            return self.mixer.forward(a, ctx, entry, writes_cache)
         if self.mixer.defers_norm and self.feed_forward.takes_deferred_norm:
             o = self.mixer.forward(a, ctx, entry, writes_cache,
                                    defer=(stream, self.norms["pre_feed_forward"]))

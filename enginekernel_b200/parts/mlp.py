@@ -1,8 +1,9 @@
-"""Gated feed-forward (SwiGLU): down(act(gate(x)) * up(x)), no biases.
+"""Gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is SiLU (SwiGLU) or the
+tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 
 engine/ek_model.py:205-209 with engine/ek_kernels.py:125-143; gate and up are
 concatenated at load (gate rows first, engine/ek_model.py:145-147).  Parameters:
-``hidden_size``, ``intermediate_size``, ``activation`` ("silu").  Tensors: ``gate``,
+``hidden_size``, ``intermediate_size``, ``activation`` ("silu", the default, or "gelu_tanh").  Tensors: ``gate``,
 ``up`` [I, H], ``down`` [H, I].
 """
 
@@ -30,9 +31,10 @@ class GatedMLP(FeedForward):
         super().__init__(spec, dtype, device)
         self.hidden = int(self.param("hidden_size"))
         self.inter = int(self.param("intermediate_size"))
-        act = spec.params.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"gated_mlp has no activation {act!r} (only silu)")
+        self.activation = spec.params.get("activation", "silu")
+        if self.activation not in kernels.GATE_ACTIVATIONS:
+            raise ValueError(f"gated_mlp has no activation {self.activation!r} "
+                             f"({', '.join(kernels.GATE_ACTIVATIONS)})")
         self.w_gate_up = self.w_down = None
 
     def load(self, tensors):
@@ -52,14 +54,16 @@ class GatedMLP(FeedForward):
         row_scale = None
         if isinstance(x, DeferredNorm):
             row_scale, x = row_scale_of(x), x.scaled
-        if self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS and tc_takes(x, self.w_gate_up):
+        fused = self.activation == "silu"        # the products' gate epilogues are SiLU
+        if fused and self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS and tc_takes(x, self.w_gate_up):
             # gate and up rows share a tile, so silu(gate) * up is formed in the epilogue
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True,
                                  row_scale=row_scale)
-        elif row_scale is not None:
+        elif row_scale is not None and not (self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS
+                                            and tc_takes(x, self.w_gate_up)):
             raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
-        elif self.dtype == torch.bfloat16 and pair_product_wins(
+        elif fused and self.dtype == torch.bfloat16 and pair_product_wins(
                 ctx.workspace.get("mlp_act", (t, self.inter), self.dtype), x, self.w_gate_up, t,
                 kernels.PAIR_EPI_SWIGLU):
             # many rows: the pair of blocks that shares a tile stages gate rows in one block and the
@@ -67,7 +71,12 @@ class GatedMLP(FeedForward):
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.gemm_pair_bf16(act, x, self.w_gate_up, kernels.PAIR_EPI_SWIGLU, n_rows=t)
         else:
-            gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
+            if row_scale is not None:
+                gu = ctx.workspace.get("mlp_gate_up", (t, 2 * self.inter), self.dtype)
+                kernels.gemm_tc_bf16(gu, x, self.w_gate_up, kernels.EPI_BF16, n_rows=t, swap=True,
+                                     row_scale=row_scale)
+            else:
+                gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
-            kernels.silu_mul(act, gu, n_rows=t)
+            kernels.act_mul(act, gu, self.activation, n_rows=t)
         return linear(act, self.w_down, ctx, "mlp_down", n_rows=t, defer=defer)

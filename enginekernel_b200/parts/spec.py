@@ -44,7 +44,7 @@ class LayerSpec:
     """One layer: a block arrangement over a mixer, a feed-forward and its norms."""
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]        # None: the layer is its mixer alone
     norms: Dict[str, PartSpec]
 
 
@@ -55,11 +55,15 @@ class RunSpec:
     ``layer`` indexes :attr:`ModelSpec.layers` (a layer may run more than once).
     ``cache`` names the cache entry its mixer uses; two runs naming the same entry
     share it, and a run with ``writes_cache=False`` only reads what another run of
-    the same step stored there.
+    the same step stored there.  ``add_embedding``: right before this run the embedding
+    output (what the stream held before the first run) is added to the stream once more -
+    for models that run a stretch of layers several times and feed the input in again at
+    the start of each further pass.
     """
     layer: int
     cache: Optional[int] = None
     writes_cache: bool = True
+    add_embedding: bool = False
 
 
 @dataclasses.dataclass(frozen=True)
@@ -78,6 +82,8 @@ class ModelSpec:
     position_table: Optional[TensorSpec] = None
     #: logits = logit_multiplier * (final norm . lm_head^T)
     logit_multiplier: float = 1.0
+    #: tensor names a checkpoint may hold although the model does not read them
+    ignorable: Tuple[str, ...] = ()
 
     def num_cache_entries(self) -> int:
         used = [r.cache for r in self.schedule if r.cache is not None]
@@ -95,6 +101,9 @@ class ModelSpec:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {run.layer}, "
                                  f"but there are {len(self.layers)} layers")
+            if run.add_embedding and i == 0:
+                raise ValueError("schedule[0] cannot add the embedding output again: the stream "
+                                 "holds nothing else yet")
             if run.cache is not None:
                 if run.cache < 0:
                     raise ValueError(f"schedule[{i}] names a negative cache entry")

@@ -55,10 +55,16 @@ def lookup_architecture(name: str):
 
 
 def architecture_of(raw_config: dict) -> str:
+    """The name that chooses the model: ``"architectures": ["<name>"]`` (the first entry), or
+    ``"architecture": "<name>"`` in files that name a single design."""
     names = raw_config.get("architectures")
-    if not (isinstance(names, list) and names and isinstance(names[0], str)):
-        raise ConfigError('config.json needs "architectures": ["<name>"] to choose the model')
-    return names[0]
+    if isinstance(names, list) and names and isinstance(names[0], str):
+        return names[0]
+    name = raw_config.get("architecture")
+    if isinstance(name, str) and name:
+        return name
+    raise ConfigError('config.json needs "architectures": ["<name>"] or "architecture": "<name>" '
+                      'to choose the model')
 
 
 def config_from_folder(path: str) -> ModelConfig:
