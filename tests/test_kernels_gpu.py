@@ -768,7 +768,7 @@ def test_launchers_refuse_what_they_cannot_do():
     with pytest.raises(KernelError):                      # inner size 12 is no multiple of 8
         k.gemm_tc_bf16(torch.empty(2, 16, dtype=torch.bfloat16, device=DEV), x, w)
     with pytest.raises(KernelError):
-        k.check_head_dim(24)
+        k.check_head_dim(264)
     with pytest.raises(KernelError):
         k.rmsnorm(torch.empty(1, 8), torch.empty(1, 8), torch.empty(8), 1e-6)   # CPU tensors
 
