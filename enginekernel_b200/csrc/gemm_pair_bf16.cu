@@ -67,6 +67,7 @@ struct PairParams {
   int tiles_m, tiles_n, n_pairs;
   int chunk, n_chunks;  // a pair takes `chunk` neighbouring column tiles of one row tile in a row (a unit)
   int swiglu_half;    // row of w where the up half starts
+  int gate_gelu;      // the gate's activation: 0 SiLU, 1 the tanh form of GELU
   int wide;           // rows of `out` (and of the cache pages) are 32-byte aligned
   int* status;
   // PAIR_EPI_QKV_ROPE: out is the q/k/v buffer [M, (NQ + 2 NKV) * 128], of which only q is written
@@ -405,7 +406,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             for (int c0 = 0; c0 < 64; c0 += 16) {
 #pragma unroll
               for (int e = 0; e < 16; ++e)
-                v[c0 + e] = __fdividef(v[c0 + e], 1.f + __expf(-v[c0 + e])) * v[64 + c0 + e];
+                v[c0 + e] = gate_fast(v[c0 + e], prm.gate_gelu) * v[64 + c0 + e];
               if (n0 + c0 + 16 <= prm.swiglu_half) {
                 store_bf16x16(o + c0, v + c0, prm.wide);
               } else {
@@ -577,12 +578,15 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, PairParams 
 }  // namespace ek
 
 // epilogue 0: out[M, N] = x . w^T in bfloat16; 1: out[M, N] (32-bit) += x . w^T; 2: out[M, N / 2] =
-// silu(x . wg^T) * (x . wu^T) in bfloat16 with w = [N / 2 gate rows; N / 2 up rows].  K, ldx, ldw
+// silu(x . wg^T) * (x . wu^T) in bfloat16 with w = [N / 2 gate rows; N / 2 up rows]; 4: the same with
+// the tanh form of GELU in place of SiLU.  K, ldx, ldw
 // must be multiples of 8, ldo of 8 (4 for the 32-bit form), the pointers 16-byte aligned.
 EK_EXPORT int ek_gemm_pair_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldw,
                                 int ldo, int epilogue, int* status, cudaStream_t stream) {
   using namespace ek;
   if (M <= 0 || N <= 0) return 0;
+  const int gate_gelu = epilogue == 4 ? 1 : 0;
+  if (gate_gelu) epilogue = PAIR_EPI_SWIGLU;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
       ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) ||
       ldo % (epilogue == PAIR_EPI_ADD_F32 ? 4 : 8) || (epilogue == PAIR_EPI_SWIGLU && (N & 1)))
@@ -592,6 +596,7 @@ EK_EXPORT int ek_gemm_pair_bf16(void* out, const void* x, const void* w, int M, 
   prm.wide = (((uintptr_t)out & 31) == 0 && ldo % (epilogue == PAIR_EPI_ADD_F32 ? 8 : 16) == 0) ? 1 : 0;
   prm.k_blocks = (K + kTcBK - 1) / kTcBK;
   prm.swiglu_half = N / 2;
+  prm.gate_gelu = gate_gelu;
   prm.tiles_m = (M + kPairTile - 1) / kPairTile;
   prm.tiles_n = epilogue == PAIR_EPI_SWIGLU ? (N / 2 + kPairRows - 1) / kPairRows : (N + kPairTile - 1) / kPairTile;
   if ((long long)prm.tiles_m * prm.tiles_n > (1ll << 30)) return EK_ERR_ARG;

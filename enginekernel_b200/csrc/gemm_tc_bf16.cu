@@ -45,8 +45,6 @@ __host__ __device__ constexpr uint32_t tc_idesc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
 }
 
-// silu for a bfloat16 result: the fast exponential and division are good to a few 32-bit ulps
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 struct TcParams {
   void* out;            // [M_out, N_out] row-major, ldo elements between rows
@@ -56,6 +54,7 @@ struct TcParams {
   int k_blocks;         // ceil(K / 64)
   int k_blocks_per_split;
   int swiglu_half;      // SwiGLU: second-half row offset in the weight matrix (I)
+  int gate_gelu;        // the gate's activation: 0 SiLU, 1 the tanh form of GELU
   float* partials;      // split-K scratch [tile][split][BN][128]
   unsigned int* tickets;
   int* status;          // 0, or the code of the first wait that timed out
@@ -86,6 +85,17 @@ struct TcParams {
   int n_q_heads;
   int write_kv;
   float qk_eps;
+  // What some designs put around that (all off when zero; same meaning as in rope_kv.cu): biases of
+  // the projections ([heads * 128], added to the 32-bit sums first), a query temperature by position,
+  // values that are the keys as projected (the weight matrix then has no value rows, and a key
+  // head goes to the value pages as it is and to the key pages normalised).  cos_tab may be null:
+  // no rotation.
+  const float* q_bias;
+  const float* k_bias;
+  const float* v_bias;
+  float q_temp_coef;
+  int q_temp_every;
+  int v_from_k;
 };
 
 // --------------------------------------------------------------------------------- kernel
@@ -299,7 +309,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       if (qkv_form && idx < owned) {
         const int pos = prm.qkv_positions[m];
         pre[ps].pos = pos;
-        if (pos >= 0 && (head_is_q || head_is_k)) {
+        if (pos >= 0 && (head_is_q || head_is_k) && prm.cos_tab != nullptr) {
           // dimension d pairs with d + 64: 16 lanes further on, same place in the lane
           pre[ps].cs = *reinterpret_cast<const float4*>(prm.cos_tab + (size_t)pos * 64 + (r0 & 63));
           pre[ps].sn = *reinterpret_cast<const float4*>(prm.sin_tab + (size_t)pos * 64 + (r0 & 63));
@@ -309,6 +319,14 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       }
     }
   };
+  // this lane's share of the head's bias (the same for every sequence)
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (qkv_form) {
+    const float* bias = head_is_q ? prm.q_bias : (head_is_k ? prm.k_bias : prm.v_bias);
+    const int local = head_is_q ? tile_p : (head_is_k ? tile_p - prm.n_q_heads : tile_p - prm.n_q_heads - prm.cache.heads);
+    if (bias != nullptr && tile_p < prm.n_q_heads + (prm.v_from_k ? 1 : 2) * prm.cache.heads)
+      bias4 = *reinterpret_cast<const float4*>(bias + (size_t)local * kTcBM + r0);
+  }
   if (SWAP && (CL || n_split == 1)) ask(0);
   bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
   tc_fence_after();
@@ -424,8 +442,8 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           if (EPI == TC_EPI_SWIGLU) {
             n_out = tile_p * 64 + r0;
             n_limit = prm.swiglu_half;
-            acc.x = silu_fast(acc.x) * up.x; acc.y = silu_fast(acc.y) * up.y;
-            acc.z = silu_fast(acc.z) * up.z; acc.w = silu_fast(acc.w) * up.w;
+            acc.x = gate_fast(acc.x, prm.gate_gelu) * up.x; acc.y = gate_fast(acc.y, prm.gate_gelu) * up.y;
+            acc.z = gate_fast(acc.z, prm.gate_gelu) * up.z; acc.w = gate_fast(acc.w, prm.gate_gelu) * up.w;
           } else {
             n_out = tile_p * kTcBM + r0;
             n_limit = prm.rows_p;
@@ -435,23 +453,38 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int head = tile_p, n_kv = prm.cache.heads;
             const int pos = pre[ps].pos;
             const bool is_q = head_is_q, is_k = head_is_k;
-            if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + 2 * n_kv) {
-              float y[4] = {acc.x, acc.y, acc.z, acc.w};
+            if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + (prm.v_from_k ? 1 : 2) * n_kv) {
+              float y[4] = {acc.x + bias4.x, acc.y + bias4.y, acc.z + bias4.z, acc.w + bias4.w};
+              if (is_k && prm.v_from_k) {        // the value: the key as projected
+                bf16* raw = (bf16*)prm.cache.v + page_offset(prm.cache, pre[ps].page, head - prm.n_q_heads, pos) + r0;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+                *reinterpret_cast<uint2*>(raw) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+              }
               if (is_q || is_k) {
                 const float* gain = is_q ? prm.q_gain : prm.k_gain;
+                float factor = 1.f;
                 if (gain != nullptr) {
                   const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
-                  const float rstd = rsqrtf(ss / 128.f + prm.qk_eps);
-                  const float4 g4 = *reinterpret_cast<const float4*>(gain + r0);
-                  y[0] = y[0] * rstd * g4.x; y[1] = y[1] * rstd * g4.y;
-                  y[2] = y[2] * rstd * g4.z; y[3] = y[3] * rstd * g4.w;
+                  factor = rsqrtf(ss / 128.f + prm.qk_eps);
                 }
-                const float4 cs = pre[ps].cs, sn = pre[ps].sn;
-                const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+                if (is_q && prm.q_temp_coef != 0.f)
+                  factor *= 1.f + prm.q_temp_coef * logf((float)((pos + 1) / prm.q_temp_every) + 1.f);
+                if (gain != nullptr) {
+                  const float4 g4 = *reinterpret_cast<const float4*>(gain + r0);
+                  y[0] = y[0] * factor * g4.x; y[1] = y[1] * factor * g4.y;
+                  y[2] = y[2] * factor * g4.z; y[3] = y[3] * factor * g4.w;
+                } else if (factor != 1.f) {
+                  y[0] *= factor; y[1] *= factor; y[2] *= factor; y[3] *= factor;
+                }
+                if (prm.cos_tab != nullptr) {
+                  const float4 cs = pre[ps].cs, sn = pre[ps].sn;
+                  const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
-                  y[i] = lane < 16 ? y[i] * c[i] - partner * sv[i] : y[i] * c[i] + partner * sv[i];
+                  for (int i = 0; i < 4; ++i) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
+                    y[i] = lane < 16 ? y[i] * c[i] - partner * sv[i] : y[i] * c[i] + partner * sv[i];
+                  }
                 }
               }
               bf16* dst;
@@ -557,7 +590,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         if (EPI == TC_EPI_SWIGLU && !SWAP) {
           fetch(c0 + BN / 2, u);               // the matching up columns
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = silu_fast(v[i]) * u[i];
+          for (int i = 0; i < 16; ++i) v[i] = gate_fast(v[i], prm.gate_gelu) * u[i];
         }
         if (EPI == TC_EPI_SWIGLU && SWAP) {
           // rows 64..127 hold the up rows of the gate rows 0..63: pass them through shared memory
@@ -569,7 +602,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           __syncthreads();
           if (row < 64) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = silu_fast(v[i]) * xch[row * 16 + i];
+            for (int i = 0; i < 16; ++i) v[i] = gate_fast(v[i], prm.gate_gelu) * xch[row * 16 + i];
           }
         }
         if (SWAP) {
@@ -695,8 +728,8 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
 
 }  // namespace ek
 
-// out[M, N] = x[M, K] . w[N, K]^T  (epilogue 0/1) or out[M, N/2] = silu(x.wg^T) * (x.wu^T) with w =
-// [gate rows; up rows] (epilogue 2).  swap != 0: weights fill the 128-row MMA side (for
+// out[M, N] = x[M, K] . w[N, K]^T  (epilogue 0/1) or out[M, N/2] = act(x.wg^T) * (x.wu^T) with w =
+// [gate rows; up rows] (epilogue 2: act = SiLU; 3: the tanh form of GELU).  swap != 0: weights fill the 128-row MMA side (for
 // 1..64 rows of x); k_split blocks share a tile's K: as a cluster if `cluster` != 0 and k_split is
 // at most 8, else through `partials` (at least tiles * k_split * bn * 128 floats) and zeroed
 // `tickets` (at least `tiles`).
@@ -709,11 +742,14 @@ static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, con
                        cudaStream_t stream) {
   using namespace ek;
   if (M <= 0 || N <= 0) return 0;
+  const int gate_gelu = epilogue == 3 ? 1 : 0;
+  if (gate_gelu) epilogue = TC_EPI_SWIGLU;     // the same tiles and epilogue, another activation
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
       (epilogue == TC_EPI_SWIGLU && (N & 1)) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   const int k_blocks = (K + kTcBK - 1) / kTcBK;
   TcParams prm = extras;
+  prm.gate_gelu = gate_gelu;
   prm.out = out; prm.ldo = ldo; prm.k_blocks = k_blocks; prm.status = status;
   prm.partials = partials; prm.tickets = tickets;
   prm.swiglu_half = N / 2;
@@ -818,6 +854,47 @@ EK_EXPORT int ek_gemm_tc_qkv_rope(void* out, const void* x, const void* w, int M
   extras.write_kv = write_kv;
   extras.qk_eps = qk_eps;
   const int N = (n_q_heads + 2 * n_kv_heads) * kTcBM;
+  if (k_split > kTcMaxCluster) k_split = kTcMaxCluster;
+  return gemm_tc_run(extras, out, x, w, M, N, K, ldx, ldw, ldo, TC_EPI_BF16, 1, k_split, 1, nullptr,
+                     nullptr, 0, 0, ss_in, ss_tiles, norm_size, eps, nullptr, 0, nullptr, nullptr, status,
+                     stream);
+}
+
+// The same product for designs that differ around it (see TcParams): biases of q, k and v (32-bit,
+// [heads * 128], nullable), a query temperature (coef 0: none), values taken from the keys as
+// projected (v_from_k: w and `out` then hold NQ + NKV heads), and no rotation when cos_tab is null.
+EK_EXPORT int ek_gemm_tc_qkv_prepare(void* out, const void* x, const void* w, int M, int K, int ldx, int ldw,
+                                     int ldo, int k_split, const float* ss_in, int ss_tiles, int norm_size,
+                                     float eps, const float* q_gain, const float* k_gain, float qk_eps,
+                                     const float* cos_tab, const float* sin_tab, const int* positions,
+                                     const int* token_slot, void* k_pages, void* v_pages,
+                                     const int* block_table, int table_stride, int n_q_heads,
+                                     int n_kv_heads, int write_kv, const float* q_bias, const float* k_bias,
+                                     const float* v_bias, float q_temp_coef, int q_temp_every, int v_from_k,
+                                     int* status, cudaStream_t stream) {
+  using namespace ek;
+  if (M <= 0) return 0;
+  if (M > 64 || n_q_heads <= 0 || n_kv_heads <= 0 || !positions || !token_slot || (!cos_tab != !sin_tab) ||
+      !k_pages || !v_pages || !block_table || ldo % 4 || ((uintptr_t)out & 7) ||
+      ((uintptr_t)cos_tab & 15) || ((uintptr_t)sin_tab & 15) || ((uintptr_t)q_gain & 15) ||
+      ((uintptr_t)k_gain & 15) || ((uintptr_t)k_pages & 7) || ((uintptr_t)v_pages & 7) ||
+      ((uintptr_t)q_bias & 15) || ((uintptr_t)k_bias & 15) || ((uintptr_t)v_bias & 15) ||
+      (q_temp_coef != 0.f && q_temp_every <= 0) || (v_from_k && v_bias))
+    return EK_ERR_ARG;
+  TcParams extras{};
+  extras.qkv_positions = positions;
+  extras.qkv_slots = token_slot;
+  extras.q_gain = q_gain;
+  extras.k_gain = k_gain;
+  extras.cos_tab = cos_tab;
+  extras.sin_tab = sin_tab;
+  extras.cache = PagedKV{k_pages, v_pages, block_table, table_stride, n_kv_heads, kTcBM};
+  extras.n_q_heads = n_q_heads;
+  extras.write_kv = write_kv;
+  extras.qk_eps = qk_eps;
+  extras.q_bias = q_bias; extras.k_bias = k_bias; extras.v_bias = v_bias;
+  extras.q_temp_coef = q_temp_coef; extras.q_temp_every = q_temp_every; extras.v_from_k = v_from_k;
+  const int N = (n_q_heads + (v_from_k ? 1 : 2) * n_kv_heads) * kTcBM;
   if (k_split > kTcMaxCluster) k_split = kTcMaxCluster;
   return gemm_tc_run(extras, out, x, w, M, N, K, ldx, ldw, ldo, TC_EPI_BF16, 1, k_split, 1, nullptr,
                      nullptr, 0, 0, ss_in, ss_tiles, norm_size, eps, nullptr, 0, nullptr, nullptr, status,

@@ -283,6 +283,121 @@ qk_norm_rope_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__
   }
 }
 
+// Wide form without rotation, with the options of QkExtras, for 16-bit rows of many tokens: a block
+// takes every head of one token, D/8 lanes a head, a lane 8 neighbouring dimensions (one 16-byte
+// load and store).  Bias, sum of squares, 1/rms times the query's temperature, gain - all in
+// 32-bit, one rounding at the end; a key head is stored twice when the values are the keys as
+// projected.  All loads of a pass are issued before the first use.
+template <int D>
+__global__ void __launch_bounds__(kWideThreads, 4)
+qk_prepare_kv_wide_kernel(bf16* qkv, int row_stride, const float* __restrict__ q_gain,
+                          const float* __restrict__ k_gain, const int* positions, const int* token_slot,
+                          PagedKV cache, int n_q_heads, float eps, int write_kv, QkExtras ex) {
+  constexpr int LPH = D / 8;                       // lanes a head
+  constexpr int HPP = kWideThreads / LPH;          // heads a pass
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int n_kv = cache.heads;
+  const int n_heads = write_kv ? n_q_heads + (ex.v_from_k ? 1 : 2) * n_kv : n_q_heads;
+  const int lih = threadIdx.x % LPH, head0 = threadIdx.x / LPH;
+  const int d0 = 8 * lih;
+  bf16* row = qkv + (size_t)t * row_stride;
+  uint4 raw[kWidePasses];
+  auto load_heads = [&](int base) {
+#pragma unroll
+    for (int p = 0; p < kWidePasses; ++p) {
+      const int head = base + p * HPP + head0;
+      if (head < n_heads) raw[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + d0);
+    }
+  };
+  load_heads(0);
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const unsigned seg = LPH == 32 ? 0xffffffffu
+                                 : ((1u << (LPH & 31)) - 1u) << ((threadIdx.x & 31) / LPH * LPH);
+  size_t page_base = 0;
+  if (write_kv) {
+    const int page = cache.block_table[(size_t)token_slot[t] * cache.table_stride + pos / EK_PAGE];
+    page_base = page_offset(cache, page, 0, pos);
+  }
+  const float temp = ex.q_temp_coef != 0.f
+                         ? 1.f + ex.q_temp_coef * logf((float)((pos + 1) / ex.q_temp_every) + 1.f) : 1.f;
+  auto eight = [&](const float* p, float* v, float fill) {
+    if (p) {
+      const float4 a = *reinterpret_cast<const float4*>(p + d0), b = *reinterpret_cast<const float4*>(p + d0 + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = fill;
+    }
+  };
+  float qg[8], kg[8];
+  eight(q_gain, qg, 1.f);
+  eight(k_gain, kg, 1.f);
+  auto pack = [](const float* y) {
+    uint4 o;
+    __nv_bfloat162 a = __floats2bfloat162_rn(y[0], y[1]), b = __floats2bfloat162_rn(y[2], y[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(y[4], y[5]), d = __floats2bfloat162_rn(y[6], y[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);
+    o.z = *reinterpret_cast<uint32_t*>(&c); o.w = *reinterpret_cast<uint32_t*>(&d);
+    return o;
+  };
+  for (int base = 0; base < n_heads; base += HPP * kWidePasses) {
+    if (base > 0) load_heads(base);
+#pragma unroll
+    for (int p = 0; p < kWidePasses; ++p) {
+      const int head = base + p * HPP + head0;
+      if (head >= n_heads) continue;               // (the D/8 lanes of a head are all in or all out)
+      const bool is_q = head < n_q_heads;
+      const bool is_k = !is_q && head < n_q_heads + n_kv;
+      const int local = is_q ? head : (is_k ? head - n_q_heads : head - n_q_heads - n_kv);
+      float x[8], b[8];
+      {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[p]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          x[2 * i] = f.x; x[2 * i + 1] = f.y;
+        }
+      }
+      const float* bias = is_q ? ex.q_bias : (is_k ? ex.k_bias : ex.v_bias);
+      eight(bias ? bias + (size_t)local * D : nullptr, b, 0.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] += b[i];
+      if (!is_q && !is_k) {                        // a value head: as projected
+        *reinterpret_cast<uint4*>((bf16*)cache.v + page_base + (size_t)local * EK_PAGE * D + d0) = pack(x);
+        continue;
+      }
+      if (is_k && ex.v_from_k)
+        *reinterpret_cast<uint4*>((bf16*)cache.v + page_base + (size_t)local * EK_PAGE * D + d0) = pack(x);
+      float factor = is_q ? temp : 1.f;
+      if (is_q ? q_gain != nullptr : k_gain != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(seg, ss, o, LPH);
+        factor *= rsqrtf(ss / (float)D + eps);
+      }
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = x[i] * factor * (is_q ? qg[i] : kg[i]);
+      bf16* dst = is_q ? row + (size_t)head * D + d0
+                       : (bf16*)cache.k + page_base + (size_t)local * EK_PAGE * D + d0;
+      *reinterpret_cast<uint4*>(dst) = pack(y);
+    }
+  }
+}
+
+template <int D>
+static int launch_prepare_wide(bf16* qkv, int row_stride, const float* q_gain, const float* k_gain,
+                               const int* positions, const int* token_slot, PagedKV cache, int n_tokens,
+                               int n_q_heads, float eps, int write_kv, QkExtras ex, cudaStream_t stream) {
+  return (int)launch_pdl(qk_prepare_kv_wide_kernel<D>, dim3(n_tokens), dim3(kWideThreads), 0, stream, qkv,
+                         row_stride, q_gain, k_gain, positions, token_slot, cache, n_q_heads, eps, write_kv, ex);
+}
+
 template <int D>
 static int launch_wide(bf16* qkv, int row_stride, const float* q_gain, const float* k_gain,
                        const float* cos_tab, const float* sin_tab, const int* positions,
@@ -322,6 +437,22 @@ static int launch(void* qkv, int row_stride, const float* q_gain, const float* k
     return EK_ERR_ARG;
   PagedKV cache{k_pages, v_pages, block_table, table_stride, n_kv_heads, head_dim};
   const bool plain = !ex.q_bias && !ex.k_bias && !ex.v_bias && ex.q_temp_coef == 0.f && !ex.v_from_k;
+  if (!plain && rot_dim == 0 && sizeof(T) == 2 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+      n_tokens >= 128 && row_stride % 8 == 0) {
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (aligned(qkv) && aligned(q_gain) && aligned(k_gain) && aligned(k_pages) && aligned(v_pages) &&
+        aligned(ex.q_bias) && aligned(ex.k_bias) && aligned(ex.v_bias)) {
+      bf16* rows = (bf16*)qkv;
+      if (head_dim == 64)
+        return launch_prepare_wide<64>(rows, row_stride, q_gain, k_gain, positions, token_slot, cache,
+                                       n_tokens, n_q_heads, eps, write_kv, ex, stream);
+      if (head_dim == 128)
+        return launch_prepare_wide<128>(rows, row_stride, q_gain, k_gain, positions, token_slot, cache,
+                                        n_tokens, n_q_heads, eps, write_kv, ex, stream);
+      return launch_prepare_wide<256>(rows, row_stride, q_gain, k_gain, positions, token_slot, cache,
+                                      n_tokens, n_q_heads, eps, write_kv, ex, stream);
+    }
+  }
   if (plain && wide_takes<T>(qkv, row_stride, q_gain, k_gain, cos_tab, sin_tab, rot_dim, k_pages, v_pages,
                     n_tokens, head_dim)) {
     bf16* rows = (bf16*)qkv;

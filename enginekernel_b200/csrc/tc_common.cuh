@@ -14,6 +14,14 @@ constexpr uint32_t kWaitLimit = 1u << 22;     // try_wait rounds before giving u
 constexpr int kMaxDevices = 64;
 constexpr int kTcBK = 64;                     // elements of a 128-byte swizzle row (bfloat16)
 
+// The gate of a gated feed-forward for a bfloat16 result: x * sigmoid(z) with z = x (SiLU) or, for
+// the tanh form of GELU, z = 2 sqrt(2/pi) (x + 0.044715 x^3), since 0.5 (1 + tanh(u)) = sigmoid(2u).
+// The fast exponential and division are good to a few 32-bit ulps.
+__device__ __forceinline__ float gate_fast(float x, int gelu_tanh) {
+  const float z = gelu_tanh ? 1.5957691216057308f * (x + 0.044715f * x * x * x) : x;
+  return __fdividef(x, 1.f + __expf(-z));
+}
+
 // ---------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);

@@ -501,7 +501,8 @@ def attention_prefill_tc(out, q, n_tokens, positions, token_slot, cu_seqlens, n_
 # ------------------------------------------------------------------ matrix products
 _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
-EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_GEGLU = 0, 1, 2, 3      # GEGLU: the gate is the tanh form of GELU
+GATED_EPILOGUES = {"silu": EPI_SWIGLU, "gelu_tanh": EPI_GEGLU}
 
 
 def gemm_f32(out, x, w, n_rows=None):
@@ -592,7 +593,7 @@ def swap_k_split(n_out, k, epilogue):
     """Blocks that share a tile's K in the swapped form: two blocks fit an SM - fill those 296
     places, keep at least 8 K blocks a block, stay within one cluster, and take a power of two
     (clusters of 3, 5, 6 or 7 blocks do not pack the GPCs evenly: 5 -> 4 was worth 0.6-1 % of a step)."""
-    tiles = -(-n_out // (64 if epilogue == EPI_SWIGLU else 128))
+    tiles = -(-n_out // (64 if epilogue in (EPI_SWIGLU, EPI_GEGLU) else 128))
     k_blocks = -(-k // 64)
     split = max(1, min(2 * sm_count() // tiles, k_blocks // 8, TC_MAX_CLUSTER))
     return 1 << (split.bit_length() - 1)
@@ -623,7 +624,7 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     _need(x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1 and x.shape[-1] == k,
           "gemm_tc_bf16: dense rows of matching inner size")
     _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tc_bf16: 16-byte aligned operands")
-    n_out = n // 2 if epilogue == EPI_SWIGLU else n
+    n_out = n // 2 if epilogue in (EPI_SWIGLU, EPI_GEGLU) else n
     _need(out.shape[-1] == n_out and out.shape[0] >= m, "gemm_tc_bf16: out shape")
     _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemm_tc_bf16: out dtype")
     if swap is None:
@@ -665,7 +666,8 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
 
 _gemm_pair = Function("gemm_pair_bf16", "ek_gemm_pair_bf16",
                       [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P])
-PAIR_EPI_BF16, PAIR_EPI_ADD_F32, PAIR_EPI_SWIGLU = 0, 1, 2
+PAIR_EPI_BF16, PAIR_EPI_ADD_F32, PAIR_EPI_SWIGLU, PAIR_EPI_GEGLU = 0, 1, 2, 4
+PAIR_GATED_EPILOGUES = {"silu": PAIR_EPI_SWIGLU, "gelu_tanh": PAIR_EPI_GEGLU}
 
 
 def gemm_pair_takes(out, x, w, epilogue) -> bool:
@@ -680,15 +682,16 @@ def gemm_pair_bf16(out, x, w, epilogue=PAIR_EPI_BF16, n_rows=None):
     """The product for many rows on pairs of SMs (``tcgen05.mma.cta_group::2``, 256 x 256 tiles, a
     persistent launch).  ``PAIR_EPI_BF16``: out [M, N] = x . w^T in bfloat16; ``PAIR_EPI_ADD_F32``:
     out [M, N] (32-bit) += x . w^T; ``PAIR_EPI_SWIGLU``: out [M, N / 2] = silu(x . wg^T) * (x . wu^T)
-    with w = [gate rows; up rows]."""
+    with w = [gate rows; up rows]; ``PAIR_EPI_GEGLU``: the same with the tanh form of GELU."""
     _need_cuda(out, x, w)
     m = n_rows if n_rows is not None else x.shape[0]
     n, k = w.shape
     _need(gemm_pair_takes(out, x, w, epilogue) and x.shape[-1] == k,
           "gemm_pair_bf16: bfloat16 operands with dense, 16-byte aligned rows of matching inner size")
-    _need(epilogue in (PAIR_EPI_BF16, PAIR_EPI_ADD_F32, PAIR_EPI_SWIGLU), "gemm_pair_bf16: epilogue")
-    _need(epilogue != PAIR_EPI_SWIGLU or n % 2 == 0, "gemm_pair_bf16: SwiGLU needs gate and up rows")
-    n_out = n // 2 if epilogue == PAIR_EPI_SWIGLU else n
+    _need(epilogue in (PAIR_EPI_BF16, PAIR_EPI_ADD_F32, PAIR_EPI_SWIGLU, PAIR_EPI_GEGLU), "gemm_pair_bf16: epilogue")
+    gated = epilogue in (PAIR_EPI_SWIGLU, PAIR_EPI_GEGLU)
+    _need(not gated or n % 2 == 0, "gemm_pair_bf16: a gated epilogue needs gate and up rows")
+    n_out = n // 2 if gated else n
     _need(out.shape[-1] == n_out and out.shape[0] >= m and x.shape[0] >= m, "gemm_pair_bf16: out shape")
     _need(out.dtype == (torch.float32 if epilogue == PAIR_EPI_ADD_F32 else torch.bfloat16),
           "gemm_pair_bf16: out dtype")
@@ -748,6 +751,67 @@ def gemm_tc_qkv_rope(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positi
                  _ptr(cos), _ptr(sin), _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
                  _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, 1 if write_kv else 0,
                  _ptr(tc_status(x.device)), _stream())
+
+
+_gemm_tc_qkv_prepare = Function("gemm_tc_bf16", "ek_gemm_tc_qkv_prepare",
+                                [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float,
+                                 _P, _P, c_float, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int,
+                                 _P, _P, _P, c_float, c_int, c_int, _P, _P])
+
+
+def gemm_tc_qkv_prepare(qkv, x, w, n_rows, q_gain, k_gain, qk_eps, cos, sin, positions, token_slot, k_pages,
+                        v_pages, block_table, n_q_heads, n_kv_heads, write_kv=True, row_scale=None,
+                        k_split=None, q_bias=None, k_bias=None, v_bias=None, q_temperature=None,
+                        values_from_keys=False):
+    """:func:`gemm_tc_qkv_rope` with the options of :func:`qk_prepare_kv` done in the product's
+    epilogue on the 32-bit sums (heads of 128, at most 64 rows): biases, the query temperature,
+    values taken from the keys as projected (``w`` and ``qkv`` then hold NQ + NKV heads).  ``cos`` and
+    ``sin`` may be None: no rotation."""
+    _need_cuda(qkv, x, w, cos, sin, positions, token_slot, k_pages, v_pages, block_table, q_bias, k_bias, v_bias)
+    m, (n, k) = n_rows, w.shape
+    heads = n_q_heads + (1 if values_from_keys else 2) * n_kv_heads
+    _need(x.dtype == w.dtype == qkv.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16,
+          "gemm_tc_qkv_prepare: bfloat16 operands, result and cache")
+    _need(m <= TC_SWAP_MAX_ROWS and n == heads * QKV_ROPE_HEAD_DIM, "gemm_tc_qkv_prepare: at most 64 rows, heads of 128")
+    _need(k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(-1) == 1
+          and w.stride(-1) == 1 and x.shape[-1] == k and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0,
+          "gemm_tc_qkv_prepare: dense, 16-byte aligned operand rows")
+    _need(qkv.stride(-1) == 1 and qkv.shape[-1] == n and qkv.stride(0) % 4 == 0 and qkv.shape[0] >= m,
+          "gemm_tc_qkv_prepare: qkv [rows, heads * 128]")
+    _need((cos is None) == (sin is None), "gemm_tc_qkv_prepare: both tables or none")
+    if cos is not None:
+        _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+              and sin.is_contiguous() and cos.shape[-1] == QKV_ROPE_HEAD_DIM // 2,
+              "gemm_tc_qkv_prepare: 32-bit tables of 64 columns")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.is_cuda and g.dtype == torch.float32 and g.numel() == QKV_ROPE_HEAD_DIM),
+              "qk gains: 32-bit [128]")
+    for b, nh in ((q_bias, n_q_heads), (k_bias, n_kv_heads), (v_bias, n_kv_heads)):
+        _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == nh * QKV_ROPE_HEAD_DIM),
+              "gemm_tc_qkv_prepare: biases are 32-bit [heads * 128]")
+    _need(not (values_from_keys and v_bias is not None), "gemm_tc_qkv_prepare: values taken from keys have no bias")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and k_pages.shape[1:] == (n_kv_heads, PAGE, QKV_ROPE_HEAD_DIM), "attention: pages [P, NKV, 64, 128]")
+    _need(block_table.dtype == torch.int32 and positions.dtype == torch.int32
+          and token_slot.dtype == torch.int32, "gemm_tc_qkv_prepare: int32 indices")
+    coef, every = (0.0, 1) if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+    _need(every >= 1, "gemm_tc_qkv_prepare: the temperature's step must be at least one position")
+    ss_in, ss_tiles, size, eps = None, 0, 0, 0.0
+    if row_scale is not None:
+        ss_in, size, eps = row_scale
+        _need(ss_in.is_cuda and ss_in.dtype == torch.float32 and ss_in.is_contiguous() and ss_in.dim() == 2
+              and ss_in.shape[0] >= m, "gemm_tc_qkv_prepare: row_scale needs 32-bit sums [rows, tiles]")
+        ss_tiles = ss_in.shape[1]
+    if k_split is None:
+        k_split = swap_k_split(n, k, EPI_BF16)
+    if lib.recording():
+        lib.annotate(bytes=2 * (n * k + m * k + m * n), flops=2 * m * n * k)
+    _gemm_tc_qkv_prepare(_ptr(qkv), _ptr(x), _ptr(w), m, k, x.stride(0), w.stride(0), qkv.stride(0), k_split,
+                         _ptr(ss_in), ss_tiles, int(size), float(eps), _ptr(q_gain), _ptr(k_gain), float(qk_eps),
+                         _ptr(cos), _ptr(sin), _ptr(positions), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages),
+                         _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, 1 if write_kv else 0,
+                         _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), coef, every, 1 if values_from_keys else 0,
+                         _ptr(tc_status(x.device)), _stream())
 
 
 _gemm_pair_qkv = Function("gemm_pair_bf16", "ek_gemm_pair_qkv_rope",

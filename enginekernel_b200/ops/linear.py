@@ -63,7 +63,8 @@ def pair_product_wins(out, x, w, m, epilogue) -> bool:
     if m <= SMALL_ROWS or not kernels.gemm_pair_takes(out, x, w, epilogue):
         return False
     n = w.shape[0]
-    n_tiles = -(-(n // 2) // 128) if epilogue == kernels.PAIR_EPI_SWIGLU else -(-n // 256)
+    n_tiles = -(-(n // 2) // 128) if epilogue in (kernels.PAIR_EPI_SWIGLU, kernels.PAIR_EPI_GEGLU) \
+        else -(-n // 256)
     return pair_fill(m, n_tiles, x.device) >= PAIR_MIN_FILL
 
 

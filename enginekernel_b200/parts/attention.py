@@ -142,6 +142,22 @@ class Attention(Mixer):
             out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
             self._attend(out, qkv, ctx, entry)
             return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+        if self._fuses_prepare(x, ctx):
+            # the same for designs with biases, a query temperature, values taken from the keys,
+            # or no rotation at all
+            row_scale, xin = (row_scale_of(x), x.scaled) if isinstance(x, DeferredNorm) else (None, x)
+            qkv = ctx.workspace.get("qkv", (t, self.w_qkv.shape[0]), self.dtype)
+            kernels.gemm_tc_qkv_prepare(
+                qkv, xin, self.w_qkv, t, self.q_gain, self.k_gain,
+                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
+                pos.cos if pos else None, pos.sin if pos else None,
+                ctx.positions, ctx.token_slot, entry.k_pages, entry.v_pages, entry.block_table,
+                self.num_heads, self.num_kv_heads, write_kv=writes_cache, row_scale=row_scale,
+                q_bias=self.bias["q"], k_bias=self.bias["k"], v_bias=self.bias["v"],
+                q_temperature=self.query_temperature, values_from_keys=self.values_from_keys)
+            out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
+            self._attend(out, qkv, ctx, entry)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
         if self._fuses_rope_of_many_rows(x, ctx):
             # many rows, heads of 128: the same on the epilogue of the product on pairs of SMs
             qkv = ctx.workspace.get("qkv", (t, self.w_qkv.shape[0]), self.dtype)
@@ -182,6 +198,14 @@ class Attention(Mixer):
         return (self._plain and self.dtype == torch.bfloat16 and ctx.n_tokens <= FUSE_ROPE_ROWS
                 and self.head_dim == kernels.QKV_ROPE_HEAD_DIM and pos is not None
                 and getattr(pos, "rotary_dim", 0) == self.head_dim and tc_takes(xin, self.w_qkv))
+
+    def _fuses_prepare(self, x, ctx):
+        xin = x.scaled if isinstance(x, DeferredNorm) else x
+        pos = self.position
+        return ((not self._plain or pos is None) and self.dtype == torch.bfloat16
+                and ctx.n_tokens <= FUSE_ROPE_ROWS and self.head_dim == kernels.QKV_ROPE_HEAD_DIM
+                and (pos is None or getattr(pos, "rotary_dim", 0) == self.head_dim)
+                and tc_takes(xin, self.w_qkv))
 
     def _fuses_rope_of_many_rows(self, x, ctx):
         pos = self.position

@@ -54,29 +54,23 @@ class GatedMLP(FeedForward):
         row_scale = None
         if isinstance(x, DeferredNorm):
             row_scale, x = row_scale_of(x), x.scaled
-        fused = self.activation == "silu"        # the products' gate epilogues are SiLU
-        if fused and self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS and tc_takes(x, self.w_gate_up):
-            # gate and up rows share a tile, so silu(gate) * up is formed in the epilogue
+        if self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS and tc_takes(x, self.w_gate_up):
+            # gate and up rows share a tile, so act(gate) * up is formed in the epilogue
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
-            kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.EPI_SWIGLU, n_rows=t, swap=True,
-                                 row_scale=row_scale)
-        elif row_scale is not None and not (self.dtype == torch.bfloat16 and t <= kernels.TC_SWAP_MAX_ROWS
-                                            and tc_takes(x, self.w_gate_up)):
+            kernels.gemm_tc_bf16(act, x, self.w_gate_up, kernels.GATED_EPILOGUES[self.activation], n_rows=t,
+                                 swap=True, row_scale=row_scale)
+        elif row_scale is not None:
             raise kernels.KernelError("a deferred norm reached a product that cannot scale its rows")
-        elif fused and self.dtype == torch.bfloat16 and pair_product_wins(
+        elif self.dtype == torch.bfloat16 and pair_product_wins(
                 ctx.workspace.get("mlp_act", (t, self.inter), self.dtype), x, self.w_gate_up, t,
-                kernels.PAIR_EPI_SWIGLU):
+                kernels.PAIR_GATED_EPILOGUES[self.activation]):
             # many rows: the pair of blocks that shares a tile stages gate rows in one block and the
-            # matching up rows in the other, and the epilogue forms silu(gate) * up from the 32-bit sums
+            # matching up rows in the other, and the epilogue forms act(gate) * up from the 32-bit sums
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
-            kernels.gemm_pair_bf16(act, x, self.w_gate_up, kernels.PAIR_EPI_SWIGLU, n_rows=t)
+            kernels.gemm_pair_bf16(act, x, self.w_gate_up, kernels.PAIR_GATED_EPILOGUES[self.activation],
+                                   n_rows=t)
         else:
-            if row_scale is not None:
-                gu = ctx.workspace.get("mlp_gate_up", (t, 2 * self.inter), self.dtype)
-                kernels.gemm_tc_bf16(gu, x, self.w_gate_up, kernels.EPI_BF16, n_rows=t, swap=True,
-                                     row_scale=row_scale)
-            else:
-                gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
+            gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.act_mul(act, gu, self.activation, n_rows=t)
         return linear(act, self.w_down, ctx, "mlp_down", n_rows=t, defer=defer)

@@ -203,6 +203,74 @@ def test_bias_head_norm_temperature_and_values_from_keys(dtype, nq, nkv, d, ever
     assert (every == 1 and first[0] > 1) or (first[0] == 1.0 and first[1] > 1.0)
 
 
+def _prepared(raw, qb, kb, qg, kg, pos_list, nq, nkv, d, coef, every, eps):
+    """What the cache and the query rows must hold, from the plain functions: (q, k normalised, v)."""
+    t = raw.shape[0]
+    q0 = raw[:, :nq * d].double().cpu() + qb.double().cpu()
+    k0 = raw[:, nq * d:].double().cpu() + kb.double().cpu()
+    qn = plain.head_norm(q0.view(t, nq, d), qg.cpu(), eps) * \
+        plain.query_temperature(pos_list, coef, every)[:, None, None]
+    return qn.reshape(t, -1), plain.head_norm(k0.view(t, nkv, d), kg.cpu(), eps), k0.view(t, nkv, d)
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(4, 2, 64), (8, 2, 128), (3, 1, 256), (40, 8, 128)])
+def test_prepare_of_many_tokens(nq, nkv, d):
+    """The form that takes a whole token a block (16-bit rows, 128 tokens and more, no rotation)."""
+    k = K()
+    dtype, coef, every, eps = torch.bfloat16, 0.4, 7, 1e-6
+    t = 333
+    pos_list = list(dict.fromkeys((i * 5) % 700 for i in range(t)))   # 140 positions, each once
+    t = len(pos_list)
+    assert t >= 128
+    pages = Pages(1, 800, nkv, d, dtype, seed=1)
+    raw = rnd(t, (nq + nkv) * d, dtype=dtype, seed=2)
+    qb, kb = rnd(nq * d, seed=3, scale=0.5), rnd(nkv * d, seed=4, scale=0.5)
+    qg, kg = 1 + 0.2 * rnd(d, seed=5), 1 + 0.2 * rnd(d, seed=6)
+    positions = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(t, dtype=torch.int32, device=DEV)
+    qkv = raw.clone()
+    empty = torch.zeros((1, 0), dtype=torch.float32, device=DEV)
+    k.qk_prepare_kv(qkv, t, qg, kg, empty, empty, 0, positions, slots, pages.k, pages.v, pages.table, nq, nkv,
+                    d, eps, q_bias=qb, k_bias=kb, q_temperature=(coef, every), values_from_keys=True)
+    qn, kn, k0 = _prepared(raw, qb, kb, qg, kg, pos_list, nq, nkv, d, coef, every, eps)
+    assert rel(qkv[:, :nq * d], qn) <= TOL[dtype]
+    kd, vd = pages.dense(0, 700)
+    idx = torch.tensor(pos_list)
+    assert rel(kd.cpu()[idx], kn) <= TOL[dtype]
+    assert rel(vd.cpu()[idx], k0) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("m,nq,nkv,hidden", [(1, 4, 2, 320), (8, 8, 2, 1024), (33, 3, 1, 136), (64, 8, 8, 512)])
+def test_projection_with_the_prepare_in_its_epilogue(m, nq, nkv, hidden):
+    """The q/k product of few rows (heads of 128) that adds the biases, normalises the heads, applies
+    the query temperature and stores keys and values itself."""
+    k = K()
+    dtype, d, coef, every, eps = torch.bfloat16, 128, 0.6, 3, 1e-5
+    pos_list = [(7 * i + 2) % 400 for i in range(m)]
+    pages = Pages(m, 400, nkv, d, dtype, seed=1)
+    x = rnd(m, hidden, dtype=dtype, seed=2)
+    w = rnd((nq + nkv) * d, hidden, dtype=dtype, seed=3, scale=hidden ** -0.5)
+    qb, kb = rnd(nq * d, seed=4, scale=0.5), rnd(nkv * d, seed=5, scale=0.5)
+    qg, kg = 1 + 0.2 * rnd(d, seed=6), 1 + 0.2 * rnd(d, seed=7)
+    positions = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    slots = torch.arange(m, dtype=torch.int32, device=DEV)
+    qkv = torch.zeros(m, (nq + nkv) * d, dtype=dtype, device=DEV)
+    for k_split in (1, 2, None):
+        pages.k.zero_()
+        pages.v.zero_()
+        k.gemm_tc_qkv_prepare(qkv, x, w, m, qg, kg, eps, None, None, positions, slots, pages.k, pages.v,
+                              pages.table, nq, nkv, k_split=k_split, q_bias=qb, k_bias=kb,
+                              q_temperature=(coef, every), values_from_keys=True)
+        k.check_tc_status(DEV)
+        raw = x.double() @ w.double().t()
+        qn, kn, k0 = _prepared(raw, qb, kb, qg, kg, pos_list, nq, nkv, d, coef, every, eps)
+        assert rel(qkv[:, :nq * d], qn) <= 4e-3, k_split
+        for i, p in enumerate(pos_list):
+            page = int(pages.table[i, p // 64])
+            assert rel(pages.k[page, :, p % 64], kn[i]) <= 4e-3
+            assert rel(pages.v[page, :, p % 64], k0[i]) <= 4e-3
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_gelu_gate_and_embedding_added_again(dtype):
     k = K()
@@ -221,6 +289,36 @@ def test_gelu_gate_and_embedding_added_again(dtype):
     k.embed(stream, table, ids, 4, scale=2.5, accumulate=True)
     assert rel(stream, 2 * first.double().cpu() + 1.0) <= 1e-6
     assert rel(first, plain.embedding(table.cpu(), ids.cpu().tolist(), 2.5)) <= 1e-6
+
+
+@pytest.mark.parametrize("m,n,k_", [(1, 256, 128), (17, 1000, 200), (64, 2560, 1024), (65, 1040, 72),
+                                    (300, 528, 200), (1000, 2048, 512)])
+def test_gelu_gate_in_the_products(m, n, k_):
+    """The gate/up product with the tanh form of GELU in its epilogue: the swapped tcgen05 form for
+    few rows (K split over a cluster, through scratch, or not), the kernel on pairs of SMs for many."""
+    k = K()
+    x = rnd(m, k_, dtype=torch.bfloat16, seed=1, scale=2.0)
+    w = rnd(n, k_, dtype=torch.bfloat16, seed=2, scale=0.05)
+    prod = x.double() @ w.double().t()
+    inter = n // 2
+    want = (plain.gelu_tanh(prod[:, :inter]) * prod[:, inter:]).cpu()
+    act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    if m <= 64:
+        for k_split, cluster in ((1, True), (3, True), (3, False), (None, True)):
+            act.fill_(9.0)
+            k.gemm_tc_bf16(act, x, w, k.EPI_GEGLU, swap=True, k_split=k_split, cluster=cluster)
+            k.check_tc_status(DEV)
+            assert rel(act, want) <= 4e-3, (k_split, cluster)
+    else:
+        k.gemm_pair_bf16(act, x, w, k.PAIR_EPI_GEGLU)
+        k.check_tc_status(DEV)
+        assert rel(act, want) <= 4e-3
+        k.gemm_tc_bf16(act, x, w, k.EPI_GEGLU, swap=False)
+        k.check_tc_status(DEV)
+        assert rel(act, want) <= 4e-3
+    # and it is not the SiLU gate
+    silu = (prod[:, :inter] / (1 + torch.exp(-prod[:, :inter])) * prod[:, inter:]).cpu()
+    assert rel(act, silu) > 2e-2
 
 
 # ===================================================================== whole models
