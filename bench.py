@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--shape 4b|8b|0.6b] [--impl ours|reference]
                     [--batch B] [--layers L] [--skip-points] [--skip-kernels]
+    python bench.py --design lopazen [--sizes 0.6b,4b,1b-h64] [--layers L] [--batch B] [--skip-kernels]
 
 The shapes and workloads are the ones BASELINE.json names (its configs[2], [3], [4]):
 
@@ -19,7 +20,10 @@ second of the whole call, the time to the first token, and the rate after the fi
 ``prefill`` is one 2,048-token prompt; ``roofline`` divides the bytes a decode step has to read
 (each weight once plus the live cache) by its time; ``kernels`` times each kernel of the decode
 step and of the prompt step on its own (:mod:`enginekernel_b200.measure`) against the measured
-peaks.  One line of JSON is printed.  The inputs of a step (gigabytes of weights) are larger than
+peaks.  ``--design lopazen`` leaves that workload alone and instead measures the Lopazen decoder
+beside the Qwen3 decoder at equal layer sizes (12 layers unless ``--layers`` says otherwise): a
+2,048-token prompt step, decode steps of a batch of 8, and both per-kernel tables for each.
+One line of JSON is printed.  The inputs of a step (gigabytes of weights) are larger than
 the L2.
 
 ``--impl reference`` runs the unmodified reference from ``baseline/_ref`` (a plain copy of its
@@ -298,6 +302,131 @@ def run_reference(args) -> int:
         shutil.rmtree(folder, ignore_errors=True)
 
 
+# --------------------------------------------------------------------------- two designs side by side
+# Layer sizes of real models (width, query heads, key heads, head size, feed-forward width); the
+# vocabulary is the Qwen3 one.  Both designs get the same sizes, layer count and workload.
+DESIGN_SIZES = {
+    "0.6b": dict(width=1024, heads=16, kv_heads=8, dim=128, ff=3072, vocab=151936),
+    "4b": dict(width=2560, heads=32, kv_heads=8, dim=128, ff=9728, vocab=151936),
+    "1b-h64": dict(width=2048, heads=32, kv_heads=8, dim=64, ff=8192, vocab=128256),
+}
+
+
+def design_configs(size: dict, layers: int, context: int):
+    """(Lopazen configuration, Qwen3 configuration) of one size."""
+    from enginekernel_b200.config import Qwen3Config
+    from enginekernel_b200.config.lopazen import LopazenConfig
+    layer = {"type": "attention",
+             "mixer": {"dim": size["dim"], "vdim": size["dim"], "heads": size["heads"],
+                       "kv_heads": size["kv_heads"], "scale": size["dim"] ** -0.5,
+                       "q_temp": {"coef": 0.5, "every": 128}},
+             "mlp": {"kind": "dense", "ff": size["ff"]}}
+    lopazen = LopazenConfig.from_dict({
+        "architecture": "Lopazen", "vocab": size["vocab"], "width": size["width"],
+        "embedding": {"scale": size["width"] ** 0.5}, "norm": {"eps": 1e-6}, "layers": [layer] * layers})
+    qwen3 = Qwen3Config.from_dict({
+        "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": layers, "hidden_size": size["width"],
+        "num_attention_heads": size["heads"], "num_key_value_heads": size["kv_heads"],
+        "head_dim": size["dim"], "intermediate_size": size["ff"], "vocab_size": size["vocab"],
+        "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+        "max_position_embeddings": context})
+    return lopazen, qwen3
+
+
+def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, with_kernels):
+    """Prompt step and decode step of one model: milliseconds, tokens a second, per-kernel tables."""
+    import torch
+    from enginekernel_b200 import Engine, SamplingParams, measure
+    from enginekernel_b200.engine.runner import StepEntry
+    engine = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=batch * context, max_batch=batch,
+                                max_len=context)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(batch)]
+    times = []
+    for it in range(3 + 5):
+        slot = engine.open_sequence()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        engine.step([(slot, prompts[0], [prompt_len - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        engine.close_sequence(slot)
+        if it >= 3:
+            times.append(a.elapsed_time(b))
+    out = {"prefill_ms": statistics.median(times)}
+    out["prefill_tok_s"] = prompt_len / (out["prefill_ms"] / 1e3)
+    room = context - prompt_len - 8
+    run = engine.backend.start(prompts, [room] * batch, SamplingParams(), [], list(range(batch)))
+    try:
+        st = run.state
+        for _ in range(warmup):
+            st.step()
+        torch.cuda.synchronize()
+        k = max(1, min(steps, room - warmup - 40))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(k):
+            st.step()
+        b.record()
+        torch.cuda.synchronize()
+        out["decode_ms"] = a.elapsed_time(b) / k
+        out["decode_tok_s"] = batch / (out["decode_ms"] / 1e3)
+        out["decode_steps"], out["launches_per_step"] = k, st.launches_per_step
+        weight_bytes = engine.model.weight_bytes_read_per_step()
+        kv = sum(2 * 2 * batch * (prompt_len + warmup + k // 2) * cs.heads * cs.head_dim
+                 for cs in engine.model.cache_entry_specs() if cs is not None)
+        out["decode_frac_of_copy_bandwidth"] = (weight_bytes + kv) / (out["decode_ms"] / 1e3) / 1e9 / pk["hbm_gbs"]
+        if with_kernels:
+            out["decode_kernels"] = measure.decode_step_table(st, pk)
+    finally:
+        run.close()
+    if with_kernels:
+        slot = engine.open_sequence()
+        try:
+            out["prefill_kernels"] = measure.prefill_step_table(
+                lambda: engine.runner.step([StepEntry(slot, prompts[0], [prompt_len - 1])]), pk)
+        finally:
+            engine.close_sequence(slot)
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_designs(args) -> int:
+    """``--design lopazen``: the Lopazen decoder beside the Qwen3 decoder at equal layer sizes."""
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"design": args.design, "unavailable": "no CUDA device here"}))
+        return 0
+    pk = peaks()
+    layers = args.layers or 12
+    batch = args.batch or 8
+    prompt_len, context = PREFILL_TOKENS, 4096
+    steps = args.steps or 128
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for name in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
+        size = DESIGN_SIZES[name]
+        lopazen, qwen3 = design_configs(size, layers, context)
+        sizes[name] = {"size": size, "layers": layers}
+        for tag, cfg in (("lopazen", lopazen), ("qwen3", qwen3)):
+            sizes[name][tag] = measure_design(cfg, size["vocab"], batch, prompt_len, context, steps,
+                                              max(3, args.warmup), pk, not args.skip_kernels)
+        a, b = sizes[name]["lopazen"], sizes[name]["qwen3"]
+        sizes[name]["lopazen_over_qwen3"] = {"prefill_tok_s": a["prefill_tok_s"] / b["prefill_tok_s"],
+                                             "decode_tok_s": a["decode_tok_s"] / b["decode_tok_s"]}
+    print(json.dumps({
+        "design": args.design, "beside": "qwen3", "dtype": "bf16", "n_gpus": 1,
+        "data": "synthetic: seeded random weights and uniform random token ids",
+        "workload": {"batch": batch, "prompt_tokens": prompt_len, "context": context, "decode_steps": steps,
+                     "prefill": "one prompt of 2,048 tokens in one step", "timing": "CUDA events",
+                     "l2": "step inputs (weights and cache of all layers) exceed the 126 MB L2"},
+        "peaks": pk, "clocks": sampler.stop(), "sizes": sizes}))
+    return 0
+
+
 # --------------------------------------------------------------------------- this repository's arm
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
@@ -313,8 +442,14 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-kernels", action="store_true", help="leave out the per-kernel tables")
     ap.add_argument("--prefill-seqs", type=int, default=1,
                     help="sequences of 2,048 tokens in the prompt step of the per-kernel table")
+    ap.add_argument("--design", default="", choices=["", "lopazen"],
+                    help="instead of the default workload: this design beside the Qwen3 decoder at "
+                         "equal layer sizes (prompt step, decode step, per-kernel tables)")
+    ap.add_argument("--sizes", default="", help="with --design: comma-separated names of DESIGN_SIZES")
     args = ap.parse_args(argv)
 
+    if args.design:
+        return run_designs(args)
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:
