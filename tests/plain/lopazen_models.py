@@ -49,7 +49,14 @@ ODD = config(72, 89, [attention_layer(3, 1, 40, 48, 0.6, 3), attention_layer(3, 
 WIDE = config(160, 301, [attention_layer(8, 2, 128, 256, 0.5, 32), attention_layer(4, 1, 128, 96, 1.0, 2)],
               loop=(0, 2, 1), scale=12.0, eps=1e-5)
 
-SHAPES = {"looped": LOOPED, "flat": FLAT, "odd": ODD, "wide": WIDE}
+# sizes that no fast path takes: a width and feed-forward sizes that are no multiples of 8, head
+# sizes 20 and 36 in different layers (so also cache groups of different shapes), 3 x 20 = 60 and
+# 2 x 36 = 72 values into the output projection, a loop that ends with the last layer
+RAGGED = config(100, 77, [attention_layer(3, 3, 20, 52, 0.5, 4), attention_layer(2, 1, 36, 30, 0.8, 9),
+                          attention_layer(6, 2, 20, None, 0.1, 2)],
+                loop=(1, 3, 2), scale=2.0, eps=1e-4)
+
+SHAPES = {"looped": LOOPED, "flat": FLAT, "odd": ODD, "wide": WIDE, "ragged": RAGGED}
 
 
 def tensor_shapes(cfg):

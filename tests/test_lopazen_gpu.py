@@ -322,7 +322,7 @@ def test_gelu_gate_in_the_products(m, n, k_):
 
 
 # ===================================================================== whole models
-SEEDS = {"looped": 11, "flat": 12, "odd": 13, "wide": 14}
+SEEDS = {"looped": 11, "flat": 12, "odd": 13, "wide": 14, "ragged": 15}
 
 
 @pytest.fixture(scope="module")
@@ -495,3 +495,47 @@ def test_a_stored_but_unused_norm_and_wrong_shapes(tmp_path):
     del w["l0.mix.k.b"]
     with pytest.raises(WeightsError, match="l0.mix.k.b"):
         Engine(models.write_folder(str(tmp_path / "b"), cfg, w), "float32", max_tokens=256, max_batch=2)
+
+
+def test_command_line_and_trace_replay(tmp_path):
+    """``random-model`` writes a Lopazen folder from a configuration file, ``generate`` prints the
+    plain model's greedy tokens for it, and ``bin/trace_run`` replays steps over the same folder."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from safetensors import safe_open
+    from tests.test_cli_gpu import ROOT, run_cli
+    cfg = models.SHAPES["odd"]
+    config_file = tmp_path / "config.json"
+    config_file.write_text(json.dumps(cfg))
+    folder = tmp_path / "model"
+    run_cli("random-model", "--config", str(config_file), "--seed", "5", "--out", str(folder))
+    with safe_open(str(folder / "model.safetensors"), framework="pt", device="cpu") as f:
+        w = {name: f.get_tensor(name) for name in f.keys()}
+    assert set(w) == set(models.tensor_shapes(cfg))
+    prompts = models.random_prompts(cfg, (3, 40), seed=4)
+    ids = ";".join(",".join(str(t) for t in p) for p in prompts)
+    out = run_cli("generate", "--model", str(folder), "--dtype", "float32", "--prompt-ids", ids, "--out-len", "5")
+    rows = [json.loads(line) for line in out.strip().splitlines()]
+    assert [r["tokens"] for r in rows] == [plain.greedy(cfg, w, p, 5) for p in prompts]
+
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": prompts[1][:30], "want": [0, 29]},
+                                     {"id": "b", "tokens": prompts[0][:1], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": prompts[1][30:31], "want": [0]},
+                                     {"id": "b", "tokens": prompts[0][1:2], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": prompts[1][31:32], "want": [0]}], "end": ["a"]}]
+    out_dir = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(folder), "--dtype",
+                        "float32", "--out", str(out_dir), "--max-tokens", "128"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                       timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    a, b = plain.logits(cfg, w, prompts[1][:32]), plain.logits(cfg, w, prompts[0][:2])
+    want = {0: torch.stack([a[0], a[29]]), 1: torch.stack([a[30], b[1]]), 2: a[31:32]}
+    for n, rows_wanted in want.items():
+        got = torch.from_numpy(np.fromfile(str(out_dir / f"{n}.f32"), dtype="<f4").reshape(rows_wanted.shape))
+        assert helpers.rel_err(got, rows_wanted) <= helpers.TOL["float32"], n
