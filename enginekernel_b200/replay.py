@@ -31,7 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at once, each rounded up to 64")
+                    help="most tokens live requests hold at once (padding to whole pages is added here)")
     args = ap.parse_args(argv)
 
     from .cache.pages import PAGE
@@ -39,9 +39,13 @@ def main(argv=None) -> int:
     from .engine.runner import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    max_tokens = max(PAGE, -(-args.max_tokens // PAGE) * PAGE)
-    engine = Engine(args.model, args.dtype, max_tokens=max_tokens,
-                    max_batch=max(1, max_tokens // PAGE))
+    # The cache hands out whole pages, so every live request may hold up to a page more than its
+    # tokens: room for that is added on top of the tokens asked for (one page per page asked for,
+    # at most 256 of them - more requests than that in flight would each fill pages of their own).
+    pages = max(1, -(-args.max_tokens // PAGE))
+    max_tokens = (pages + min(pages, 256)) * PAGE
+    engine = Engine(args.model, args.dtype, max_tokens=max_tokens, max_batch=max(1, max_tokens // PAGE),
+                    max_len=pages * PAGE)
     slots = {}
     for line in sys.stdin:
         line = line.strip()
