@@ -34,7 +34,9 @@
 
 namespace ek {
 
-enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2 };
+// (TC_EPI_QKVX: the bfloat16 epilogue of the q/k/v product in its extended form - an instantiation of its
+// own, so that the kernels of designs without those options stay as they are, instruction for instruction)
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2, TC_EPI_QKVX = 4 };
 
 constexpr int kTcBM = 128;                    // rows of P per tile (TMEM lanes)
 constexpr int kTcPushRows = 8;               // sequences whose partial sums are sent, not fetched
@@ -290,7 +292,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const int owned = prm.rows_q > first ? (prm.rows_q - first + step - 1) / step : 0;
   const int sub = lane / (R / 4), r0 = 4 * (lane % (R / 4));
   const bool fused_add = EPI == TC_EPI_BF16 && prm.stream != nullptr;
-  const bool qkv_form = EPI == TC_EPI_BF16 && prm.qkv_positions != nullptr;
+  const bool qkv_form = (EPI == TC_EPI_BF16 || EPI == TC_EPI_QKVX) && prm.qkv_positions != nullptr;
   const bool head_is_q = tile_p < prm.n_q_heads, head_is_k = !head_is_q && tile_p < prm.n_q_heads + prm.cache.heads;
   struct Asked { float4 st, gn, cs, sn; int pos, page; };
   Asked pre[P];
@@ -309,7 +311,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       if (qkv_form && idx < owned) {
         const int pos = prm.qkv_positions[m];
         pre[ps].pos = pos;
-        if (pos >= 0 && (head_is_q || head_is_k) && prm.cos_tab != nullptr) {
+        if (pos >= 0 && (head_is_q || head_is_k) && (EPI != TC_EPI_QKVX || prm.cos_tab != nullptr)) {
           // dimension d pairs with d + 64: 16 lanes further on, same place in the lane
           pre[ps].cs = *reinterpret_cast<const float4*>(prm.cos_tab + (size_t)pos * 64 + (r0 & 63));
           pre[ps].sn = *reinterpret_cast<const float4*>(prm.sin_tab + (size_t)pos * 64 + (r0 & 63));
@@ -319,14 +321,6 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       }
     }
   };
-  // this lane's share of the head's bias (the same for every sequence)
-  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (qkv_form) {
-    const float* bias = head_is_q ? prm.q_bias : (head_is_k ? prm.k_bias : prm.v_bias);
-    const int local = head_is_q ? tile_p : (head_is_k ? tile_p - prm.n_q_heads : tile_p - prm.n_q_heads - prm.cache.heads);
-    if (bias != nullptr && tile_p < prm.n_q_heads + (prm.v_from_k ? 1 : 2) * prm.cache.heads)
-      bias4 = *reinterpret_cast<const float4*>(bias + (size_t)local * kTcBM + r0);
-  }
   if (SWAP && (CL || n_split == 1)) ask(0);
   bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
   tc_fence_after();
@@ -448,13 +442,23 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             n_out = tile_p * kTcBM + r0;
             n_limit = prm.rows_p;
           }
-          if (qkv_form) {
+          if (qkv_form && EPI == TC_EPI_QKVX) {
+            // the form with biases, a query temperature, values from keys, an optional rotation
             // head = tile; everything below is uniform over the warp except the lane's 4 dimensions
             const int head = tile_p, n_kv = prm.cache.heads;
             const int pos = pre[ps].pos;
             const bool is_q = head_is_q, is_k = head_is_k;
             if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + (prm.v_from_k ? 1 : 2) * n_kv) {
-              float y[4] = {acc.x + bias4.x, acc.y + bias4.y, acc.z + bias4.z, acc.w + bias4.w};
+              float y[4] = {acc.x, acc.y, acc.z, acc.w};
+              {
+                // the bias is asked for here, not ahead of the accumulator: designs without one pay nothing
+                const float* bias = is_q ? prm.q_bias : (is_k ? prm.k_bias : prm.v_bias);
+                if (bias != nullptr) {
+                  const int local = is_q ? head : (is_k ? head - prm.n_q_heads : head - prm.n_q_heads - n_kv);
+                  const float4 b4 = *reinterpret_cast<const float4*>(bias + (size_t)local * kTcBM + r0);
+                  y[0] += b4.x; y[1] += b4.y; y[2] += b4.z; y[3] += b4.w;
+                }
+              }
               if (is_k && prm.v_from_k) {        // the value: the key as projected
                 bf16* raw = (bf16*)prm.cache.v + page_offset(prm.cache, pre[ps].page, head - prm.n_q_heads, pos) + r0;
                 __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
@@ -485,6 +489,42 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
                     y[i] = lane < 16 ? y[i] * c[i] - partner * sv[i] : y[i] * c[i] + partner * sv[i];
                   }
+                }
+              }
+              bf16* dst;
+              if (is_q) {
+                dst = (bf16*)prm.out + (size_t)m * prm.ldo + n_out;
+              } else {
+                const int page = pre[ps].page;
+                const int kv_head = is_k ? head - prm.n_q_heads : head - prm.n_q_heads - n_kv;
+                dst = (bf16*)(is_k ? prm.cache.k : prm.cache.v) + page_offset(prm.cache, page, kv_head, pos) + r0;
+              }
+              __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+              *reinterpret_cast<uint2*>(dst) =
+                  make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+          } else if (qkv_form) {
+            // head = tile; everything below is uniform over the warp except the lane's 4 dimensions
+            const int head = tile_p, n_kv = prm.cache.heads;
+            const int pos = pre[ps].pos;
+            const bool is_q = head_is_q, is_k = head_is_k;
+            if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + 2 * n_kv) {
+              float y[4] = {acc.x, acc.y, acc.z, acc.w};
+              if (is_q || is_k) {
+                const float* gain = is_q ? prm.q_gain : prm.k_gain;
+                if (gain != nullptr) {
+                  const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+                  const float rstd = rsqrtf(ss / 128.f + prm.qk_eps);
+                  const float4 g4 = *reinterpret_cast<const float4*>(gain + r0);
+                  y[0] = y[0] * rstd * g4.x; y[1] = y[1] * rstd * g4.y;
+                  y[2] = y[2] * rstd * g4.z; y[3] = y[3] * rstd * g4.w;
+                }
+                const float4 cs = pre[ps].cs, sn = pre[ps].sn;
+                const float c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
+                  y[i] = lane < 16 ? y[i] * c[i] - partner * sv[i] : y[i] * c[i] + partner * sv[i];
                 }
               }
               bf16* dst;
@@ -744,7 +784,8 @@ static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, con
   if (M <= 0 || N <= 0) return 0;
   const int gate_gelu = epilogue == 3 ? 1 : 0;
   if (gate_gelu) epilogue = TC_EPI_SWIGLU;     // the same tiles and epilogue, another activation
-  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 || epilogue > 2 ||
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 ||
+      (epilogue > 2 && !(epilogue == TC_EPI_QKVX && swap && extras.qkv_positions)) ||
       (epilogue == TC_EPI_SWIGLU && (N & 1)) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   const int k_blocks = (K + kTcBK - 1) / kTcBK;
@@ -786,11 +827,13 @@ static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, con
   if (bn == BN && clustered) {                                                                   \
     if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, true, true>(mp, mq, prm, grid, stream); \
     if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, true, true>(mp, mq, prm, grid, stream);   \
+    if (epilogue == TC_EPI_QKVX) return launch_tc<BN, TC_EPI_QKVX, true, true>(mp, mq, prm, grid, stream); \
     return launch_tc<BN, TC_EPI_SWIGLU, true, true>(mp, mq, prm, grid, stream);                  \
   }                                                                                              \
   if (bn == BN) {                                                                                \
     if (epilogue == TC_EPI_BF16) return launch_tc<BN, TC_EPI_BF16, true>(mp, mq, prm, grid, stream); \
     if (epilogue == TC_EPI_F32) return launch_tc<BN, TC_EPI_F32, true>(mp, mq, prm, grid, stream);   \
+    if (epilogue == TC_EPI_QKVX) return launch_tc<BN, TC_EPI_QKVX, true>(mp, mq, prm, grid, stream); \
     return launch_tc<BN, TC_EPI_SWIGLU, true>(mp, mq, prm, grid, stream);                        \
   }
     EK_SWAP(16) EK_SWAP(32) EK_SWAP(64)
@@ -896,7 +939,7 @@ EK_EXPORT int ek_gemm_tc_qkv_prepare(void* out, const void* x, const void* w, in
   extras.q_temp_coef = q_temp_coef; extras.q_temp_every = q_temp_every; extras.v_from_k = v_from_k;
   const int N = (n_q_heads + (v_from_k ? 1 : 2) * n_kv_heads) * kTcBM;
   if (k_split > kTcMaxCluster) k_split = kTcMaxCluster;
-  return gemm_tc_run(extras, out, x, w, M, N, K, ldx, ldw, ldo, TC_EPI_BF16, 1, k_split, 1, nullptr,
+  return gemm_tc_run(extras, out, x, w, M, N, K, ldx, ldw, ldo, TC_EPI_QKVX, 1, k_split, 1, nullptr,
                      nullptr, 0, 0, ss_in, ss_tiles, norm_size, eps, nullptr, 0, nullptr, nullptr, status,
                      stream);
 }
