@@ -363,18 +363,23 @@ def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, wi
         for _ in range(warmup):
             st.step()
         torch.cuda.synchronize()
-        k = max(1, min(steps, room - warmup - 40))
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(k):
-            st.step()
-        b.record()
-        torch.cuda.synchronize()
-        out["decode_ms"] = a.elapsed_time(b) / k
+        stretches = 5                                # median of five stretches of k steps
+        k = max(1, min(steps, (room - warmup - 40) // stretches))
+        per_step = []
+        for _ in range(stretches):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(k):
+                st.step()
+            b.record()
+            torch.cuda.synchronize()
+            per_step.append(a.elapsed_time(b) / k)
+        out["decode_ms"] = statistics.median(per_step)
+        out["decode_ms_spread"] = [min(per_step), max(per_step)]
         out["decode_tok_s"] = batch / (out["decode_ms"] / 1e3)
         out["decode_steps"], out["launches_per_step"] = k, st.launches_per_step
         weight_bytes = engine.model.weight_bytes_read_per_step()
-        kv = sum(2 * 2 * batch * (prompt_len + warmup + k // 2) * cs.heads * cs.head_dim
+        kv = sum(2 * 2 * batch * (prompt_len + warmup + stretches * k // 2) * cs.heads * cs.head_dim
                  for cs in engine.model.cache_entry_specs() if cs is not None)
         out["decode_frac_of_copy_bandwidth"] = (weight_bytes + kv) / (out["decode_ms"] / 1e3) / 1e9 / pk["hbm_gbs"]
         if with_kernels:
@@ -420,7 +425,7 @@ def run_designs(args) -> int:
     print(json.dumps({
         "design": args.design, "beside": "qwen3", "dtype": "bf16", "n_gpus": 1,
         "data": "synthetic: seeded random weights and uniform random token ids",
-        "workload": {"batch": batch, "prompt_tokens": prompt_len, "context": context, "decode_steps": steps,
+        "workload": {"batch": batch, "prompt_tokens": prompt_len, "context": context, "decode_steps": f"median of 5 stretches of {steps}",
                      "prefill": "one prompt of 2,048 tokens in one step", "timing": "CUDA events",
                      "l2": "step inputs (weights and cache of all layers) exceed the 126 MB L2"},
         "peaks": pk, "clocks": sampler.stop(), "sizes": sizes}))

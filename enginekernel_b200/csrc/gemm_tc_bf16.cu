@@ -34,8 +34,11 @@
 
 namespace ek {
 
-// (TC_EPI_QKVX: the bfloat16 epilogue of the q/k/v product in its extended form - an instantiation of its
-// own, so that the kernels of designs without those options stay as they are, instruction for instruction)
+// (TC_EPI_QKVX: the bfloat16 epilogue with the q/k/v product's extended form in it - an instantiation of
+// its own, so that the kernels of designs without those options stay as they are, instruction for
+// instruction.  It does everything TC_EPI_BF16 does, and a model whose q/k/v product needs it runs its
+// other bfloat16 products of few rows through it too: one kernel's code then stays in the instruction
+// caches from product to product, which is worth 5 % of a decode step at width 1,024.)
 enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2, TC_EPI_QKVX = 4 };
 
 constexpr int kTcBM = 128;                    // rows of P per tile (TMEM lanes)
@@ -291,7 +294,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
   const int step = CL ? n_split : 1, first = CL ? split : 0;
   const int owned = prm.rows_q > first ? (prm.rows_q - first + step - 1) / step : 0;
   const int sub = lane / (R / 4), r0 = 4 * (lane % (R / 4));
-  const bool fused_add = EPI == TC_EPI_BF16 && prm.stream != nullptr;
+  const bool fused_add = (EPI == TC_EPI_BF16 || EPI == TC_EPI_QKVX) && prm.stream != nullptr;
   const bool qkv_form = (EPI == TC_EPI_BF16 || EPI == TC_EPI_QKVX) && prm.qkv_positions != nullptr;
   const bool head_is_q = tile_p < prm.n_q_heads, head_is_k = !head_is_q && tile_p < prm.n_q_heads + prm.cache.heads;
   struct Asked { float4 st, gn, cs, sn; int pos, page; };
@@ -321,6 +324,15 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       }
     }
   };
+  // the extended q/k/v form: this lane's share of the head's bias (the same for every sequence),
+  // asked for while the MMAs still run, like the rest
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (EPI == TC_EPI_QKVX && qkv_form) {
+    const float* bias = head_is_q ? prm.q_bias : (head_is_k ? prm.k_bias : prm.v_bias);
+    const int local = head_is_q ? tile_p : (head_is_k ? tile_p - prm.n_q_heads : tile_p - prm.n_q_heads - prm.cache.heads);
+    if (bias != nullptr && tile_p < prm.n_q_heads + (prm.v_from_k ? 1 : 2) * prm.cache.heads)
+      bias4 = *reinterpret_cast<const float4*>(bias + (size_t)local * kTcBM + r0);
+  }
   if (SWAP && (CL || n_split == 1)) ask(0);
   bool acc_ok = n_iter > 0 ? mbar_wait(accum_bar, 0, prm.status, 3) : true;
   tc_fence_after();
@@ -449,16 +461,7 @@ gemm_tc_bf16_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             const int pos = pre[ps].pos;
             const bool is_q = head_is_q, is_k = head_is_k;
             if (pos >= 0 && (is_q || prm.write_kv) && head < prm.n_q_heads + (prm.v_from_k ? 1 : 2) * n_kv) {
-              float y[4] = {acc.x, acc.y, acc.z, acc.w};
-              {
-                // the bias is asked for here, not ahead of the accumulator: designs without one pay nothing
-                const float* bias = is_q ? prm.q_bias : (is_k ? prm.k_bias : prm.v_bias);
-                if (bias != nullptr) {
-                  const int local = is_q ? head : (is_k ? head - prm.n_q_heads : head - prm.n_q_heads - n_kv);
-                  const float4 b4 = *reinterpret_cast<const float4*>(bias + (size_t)local * kTcBM + r0);
-                  y[0] += b4.x; y[1] += b4.y; y[2] += b4.z; y[3] += b4.w;
-                }
-              }
+              float y[4] = {acc.x + bias4.x, acc.y + bias4.y, acc.z + bias4.z, acc.w + bias4.w};
               if (is_k && prm.v_from_k) {        // the value: the key as projected
                 bf16* raw = (bf16*)prm.cache.v + page_offset(prm.cache, pre[ps].page, head - prm.n_q_heads, pos) + r0;
                 __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
@@ -769,7 +772,8 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, const TcParam
 }  // namespace ek
 
 // out[M, N] = x[M, K] . w[N, K]^T  (epilogue 0/1) or out[M, N/2] = act(x.wg^T) * (x.wu^T) with w =
-// [gate rows; up rows] (epilogue 2: act = SiLU; 3: the tanh form of GELU).  swap != 0: weights fill the 128-row MMA side (for
+// [gate rows; up rows] (epilogue 2: act = SiLU; 3: the tanh form of GELU).  Epilogue 4 (swapped form only)
+// is epilogue 0 computed by the instantiation that also holds the extended q/k/v epilogue.  swap != 0: weights fill the 128-row MMA side (for
 // 1..64 rows of x); k_split blocks share a tile's K: as a cluster if `cluster` != 0 and k_split is
 // at most 8, else through `partials` (at least tiles * k_split * bn * 128 floats) and zeroed
 // `tickets` (at least `tiles`).
@@ -785,7 +789,7 @@ static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, con
   const int gate_gelu = epilogue == 3 ? 1 : 0;
   if (gate_gelu) epilogue = TC_EPI_SWIGLU;     // the same tiles and epilogue, another activation
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !status || epilogue < 0 ||
-      (epilogue > 2 && !(epilogue == TC_EPI_QKVX && swap && extras.qkv_positions)) ||
+      (epilogue > 2 && !(epilogue == TC_EPI_QKVX && swap)) ||
       (epilogue == TC_EPI_SWIGLU && (N & 1)) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   const int k_blocks = (K + kTcBK - 1) / kTcBK;
@@ -798,7 +802,7 @@ static int gemm_tc_run(const ek::TcParams& extras, void* out, const void* x, con
   prm.ss_inv_size = norm_size > 0 ? 1.f / (float)norm_size : 0.f;
   prm.stream = residual; prm.ld_stream = ld_residual; prm.next_gain = next_gain; prm.ss_out = ss_out;
   if (ss_in && (!swap || ss_tiles <= 0 || norm_size <= 0)) return EK_ERR_ARG;
-  if (residual && (!swap || epilogue != TC_EPI_BF16 || !next_gain || !ss_out || N % 4 || ldo % 4 ||
+  if (residual && (!swap || (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_QKVX) || !next_gain || !ss_out || N % 4 || ldo % 4 ||
                    ld_residual % 4 || ((uintptr_t)residual & 15) || ((uintptr_t)next_gain & 15) ||
                    ((uintptr_t)out & 7)))
     return EK_ERR_ARG;

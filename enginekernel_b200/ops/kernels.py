@@ -503,6 +503,10 @@ _gemm_f32 = Function("gemm_f32", "ek_gemm_nt_f32",
                      [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P])
 EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_GEGLU = 0, 1, 2, 3      # GEGLU: the gate is the tanh form of GELU
 GATED_EPILOGUES = {"silu": EPI_SWIGLU, "gelu_tanh": EPI_GEGLU}
+# EPI_BF16 computed by the compiled image that also holds the extended q/k/v epilogue (swapped form):
+# for the other few-row products of a model whose q/k/v product runs there, so that one kernel's code
+# serves them all (see Mixer.product_image)
+EPI_BF16_EXTENDED = 4
 
 
 def gemm_f32(out, x, w, n_rows=None):
@@ -629,6 +633,7 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     _need(out.dtype == (torch.float32 if epilogue == EPI_F32 else torch.bfloat16), "gemm_tc_bf16: out dtype")
     if swap is None:
         swap = m <= TC_SWAP_MAX_ROWS
+    _need(epilogue != EPI_BF16_EXTENDED or swap, "gemm_tc_bf16: the extended image is a swapped form")
     _need(not swap or m <= TC_SWAP_MAX_ROWS, "gemm_tc_bf16: the swapped form takes at most 64 rows")
     partials, tickets = split_scratch(x.device)
     if k_split is None:
@@ -645,7 +650,7 @@ def gemm_tc_bf16(out, x, w, epilogue=EPI_BF16, n_rows=None, swap=None, k_split=N
     if residual is not None:
         stream, gain, ss_out = residual
         _need_cuda(stream, gain, ss_out)
-        _need(swap and epilogue == EPI_BF16 and n % 4 == 0 and out.stride(0) % 4 == 0,
+        _need(swap and epilogue in (EPI_BF16, EPI_BF16_EXTENDED) and n % 4 == 0 and out.stride(0) % 4 == 0,
               "gemm_tc_bf16: residual needs the swapped form, a bfloat16 result and N a multiple of 4")
         _need(stream.dtype == torch.float32 and stream.stride(-1) == 1 and stream.stride(0) % 4 == 0
               and stream.shape[-1] == n and stream.shape[0] >= m and stream.data_ptr() % 16 == 0,

@@ -68,7 +68,7 @@ def pair_product_wins(out, x, w, m, epilogue) -> bool:
     return pair_fill(m, n_tiles, x.device) >= PAIR_MIN_FILL
 
 
-def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
+def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None, image=None):
     """``x`` [M, K] (dense rows), ``w`` [N, K] -> [M, N] from the step's workspace.
 
     ``x`` may be a :class:`~enginekernel_b200.parts.base.DeferredNorm` (the product scales its
@@ -76,7 +76,10 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
     ``norm`` next, and this product may do part of that: with few rows the result is added to
     ``stream`` here and a DeferredNorm for ``norm`` is returned; with many rows (bfloat16) the
     product adds its 32-bit result to ``stream`` and None is returned (nothing left to add: the
-    norm is called without ``add``).  Otherwise the plain result comes back."""
+    norm is called without ``add``).  Otherwise the plain result comes back.
+    ``image="extended"``: few-row bfloat16 products go through the compiled image that also holds the
+    extended q/k/v epilogue (see :meth:`~enginekernel_b200.parts.base.Mixer.product_image`)."""
+    epi_bf16 = kernels.EPI_BF16_EXTENDED if image == "extended" else kernels.EPI_BF16
     from ..parts.base import DeferredNorm
     row_scale = None
     if isinstance(x, DeferredNorm):
@@ -92,7 +95,7 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
             tiles = -(-n // 128)
             scaled = ctx.workspace.get("deferred_" + name, (m, n), torch.bfloat16)
             ss = ctx.workspace.get("deferred_ss_" + name, (m, tiles), torch.float32)
-            kernels.gemm_tc_bf16(scaled, x, w, kernels.EPI_BF16, n_rows=m, swap=True,
+            kernels.gemm_tc_bf16(scaled, x, w, epi_bf16, n_rows=m, swap=True,
                                  row_scale=row_scale, residual=(stream, gain, ss))
             return DeferredNorm(scaled, ss, tiles, n, float(eps))
     if (defer is not None and row_scale is None and out_dtype is None and w.dtype == torch.bfloat16
@@ -125,7 +128,7 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None):
             _library_product(x[:m], w, out)
         return out
     if m <= SMALL_ROWS:
-        kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=True, row_scale=row_scale)
+        kernels.gemm_tc_bf16(out, x, w, epi if want_f32 else epi_bf16, n_rows=m, swap=True, row_scale=row_scale)
     elif want_f32:
         # 32-bit logits for many rows: 128 x 128 tiles with the accumulator stored as it is
         kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=False)

@@ -141,7 +141,7 @@ class Attention(Mixer):
                 self.num_heads, self.num_kv_heads, write_kv=writes_cache, row_scale=row_scale)
             out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
             self._attend(out, qkv, ctx, entry)
-            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer, image=self.product_image())
         if self._fuses_prepare(x, ctx):
             # the same for designs with biases, a query temperature, values taken from the keys,
             # or no rotation at all
@@ -157,7 +157,7 @@ class Attention(Mixer):
                 q_temperature=self.query_temperature, values_from_keys=self.values_from_keys)
             out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
             self._attend(out, qkv, ctx, entry)
-            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer, image=self.product_image())
         if self._fuses_rope_of_many_rows(x, ctx):
             # many rows, heads of 128: the same on the epilogue of the product on pairs of SMs
             qkv = ctx.workspace.get("qkv", (t, self.w_qkv.shape[0]), self.dtype)
@@ -168,7 +168,7 @@ class Attention(Mixer):
                 self.num_heads, self.num_kv_heads, write_kv=writes_cache)
             out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
             self._attend(out, qkv, ctx, entry)
-            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+            return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer, image=self.product_image())
         qkv = linear(x, self.w_qkv, ctx, "qkv", n_rows=t)
         prepare = (qkv, t, self.q_gain, self.k_gain,
                    pos.cos if pos else _no_table(self.device), pos.sin if pos else _no_table(self.device),
@@ -184,7 +184,7 @@ class Attention(Mixer):
                                   values_from_keys=self.values_from_keys)
         out = ctx.workspace.get("attn_out", (t, self.num_heads * self.head_dim), self.dtype)
         self._attend(out, qkv, ctx, entry)
-        return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer)
+        return linear(out, self.w_o, ctx, "attn_proj", n_rows=t, defer=defer, image=self.product_image())
 
     @property
     def _plain(self):
@@ -199,12 +199,18 @@ class Attention(Mixer):
                 and self.head_dim == kernels.QKV_ROPE_HEAD_DIM and pos is not None
                 and getattr(pos, "rotary_dim", 0) == self.head_dim and tc_takes(xin, self.w_qkv))
 
+    def product_image(self):
+        """``"extended"`` when this layer's q/k/v product of few rows runs the extended epilogue."""
+        pos = self.position
+        if ((not self._plain or pos is None) and self.dtype == torch.bfloat16
+                and self.head_dim == kernels.QKV_ROPE_HEAD_DIM
+                and (pos is None or getattr(pos, "rotary_dim", 0) == self.head_dim)):
+            return "extended"
+        return None
+
     def _fuses_prepare(self, x, ctx):
         xin = x.scaled if isinstance(x, DeferredNorm) else x
-        pos = self.position
-        return ((not self._plain or pos is None) and self.dtype == torch.bfloat16
-                and ctx.n_tokens <= FUSE_ROPE_ROWS and self.head_dim == kernels.QKV_ROPE_HEAD_DIM
-                and (pos is None or getattr(pos, "rotary_dim", 0) == self.head_dim)
+        return (self.product_image() == "extended" and ctx.n_tokens <= FUSE_ROPE_ROWS
                 and tc_takes(xin, self.w_qkv))
 
     def _fuses_rope_of_many_rows(self, x, ctx):

@@ -175,6 +175,13 @@ class Mixer(Part):
     def prepare(self, max_positions: int) -> None:
         """Called once the longest position is known (tables and the like)."""
 
+    def product_image(self) -> Optional[str]:
+        """Which compiled image of the few-row bfloat16 product this mixer's own products run on
+        (None: the plain one; ``"extended"``: the one that also holds the extended q/k/v epilogue).
+        A block hands the answer to its feed-forward, so that a layer's products share one kernel's
+        code wherever they can."""
+        return None
+
     def begin_step(self, ctx: StepContext) -> None:
         """Called for every scheduled mixer before the step's first kernel: the place for what
         depends on the step's sequences but not on the layer (put it into ``ctx.shared``).
@@ -188,6 +195,8 @@ class FeedForward(Part):
     role = "feed_forward"
     takes_deferred_norm = False
     defers_norm = False
+    #: set by the block from its mixer's :meth:`Mixer.product_image`
+    product_image: Optional[str] = None
 
     def forward(self, x, ctx: StepContext):
         raise NotImplementedError
@@ -201,6 +210,8 @@ class Block(Part):
                  norms: Dict[str, Norm]):
         super().__init__(spec, dtype, device)
         self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+        if feed_forward is not None:
+            feed_forward.product_image = mixer.product_image()
 
     @classmethod
     def norm_names(cls, spec: PartSpec) -> List[str]:

@@ -73,4 +73,4 @@ class GatedMLP(FeedForward):
             gu = linear(x, self.w_gate_up, ctx, "mlp_gate_up", n_rows=t)
             act = ctx.workspace.get("mlp_act", (t, self.inter), self.dtype)
             kernels.act_mul(act, gu, self.activation, n_rows=t)
-        return linear(act, self.w_down, ctx, "mlp_down", n_rows=t, defer=defer)
+        return linear(act, self.w_down, ctx, "mlp_down", n_rows=t, defer=defer, image=self.product_image)
