@@ -2,7 +2,8 @@
 
 Cache entries (one per scheduled mixer that keeps something) with equal
 :class:`~enginekernel_b200.parts.spec.CacheSpec` form a group.  A ``kv`` group owns
-``pages[entry, k|v, page, kv_head, PAGE, head_dim]`` in the engine's dtype and a block
+``pages[entry, k|v, page, kv_head, PAGE, head_dim]`` (one plane instead of two where the spec says so)
+in the engine's dtype and a block
 table ``[slot, logical page] -> page``; a ``state`` group owns
 ``data[entry, slot, *shape]``, zeroed whenever a sequence takes the slot.  Sizes are fixed
 at construction from the number of tokens to hold (``max_tokens``, counted per sequence
@@ -39,7 +40,8 @@ class EntryView:
 
     @property
     def v_pages(self):
-        return self._group.pages[self._i, 1]
+        """The value pages; with one plane per token (``CacheSpec.planes == 1``) the key pages again."""
+        return self._group.pages[self._i, self._group.pages.shape[1] - 1]
 
     @property
     def block_table(self):
@@ -59,7 +61,7 @@ class GroupStorage:
         self.pages = self.block_table = self.data = None
         if spec.kind == "kv":
             self.page_group = PageGroup(num_pages, num_slots, max_pages_per_slot, spec.window)
-            self.pages = torch.zeros((len(entries), 2, num_pages, spec.heads, PAGE, spec.head_dim),
+            self.pages = torch.zeros((len(entries), spec.planes, num_pages, spec.heads, PAGE, spec.head_dim),
                                      dtype=dtype, device=device)
             self.block_table = torch.zeros((num_slots, max_pages_per_slot), dtype=torch.int32,
                                            device=device)

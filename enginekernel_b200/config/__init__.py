@@ -2,5 +2,6 @@
 from .base import ConfigError, ModelConfig, key, read_config_json
 from .lopazen import LopazenConfig
 from .qwen3 import Qwen3Config
+from .susalorn import SusalornConfig
 
-__all__ = ["ConfigError", "LopazenConfig", "ModelConfig", "Qwen3Config", "key", "read_config_json"]
+__all__ = ["ConfigError", "LopazenConfig", "ModelConfig", "Qwen3Config", "SusalornConfig", "key", "read_config_json"]

@@ -59,7 +59,7 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
                              PagedKV cache, int n_q_heads, int row_blocks, float scale_log2,
                              int window, int n_splits, int keys_per_split,
                              float* __restrict__ part_acc, float* __restrict__ part_ml,
-                             float sink_log2) {
+                             float sink_log2, const float* __restrict__ sinks) {
   constexpr int D = DCH * 32;
   extern __shared__ float smem[];              // [warps][16][D] accumulators, then [warps][16][2]
   float* o_s = smem;
@@ -234,7 +234,8 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
     const int head = head0 + r;
     if (n_splits == 1) {
       // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
-      if (sink_log2 > -INFINITY && l > 0.f) l += exp2f(sink_log2 - m);
+      const float sk = sinks ? sinks[head] * 1.4426950408889634f : sink_log2;   // per head, if given
+      if (sk > -INFINITY && l > 0.f) l += exp2f(sk - m);
       out[((size_t)t * n_q_heads + head) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     } else {
       const size_t pi = ((size_t)t * n_q_heads + head) * n_splits + split;
@@ -251,7 +252,9 @@ attention_decode_bf16_kernel(bf16* __restrict__ out, const bf16* q, int q_row_st
 __global__ void attention_decode_combine_kernel(bf16* __restrict__ out,
                                                 const float* part_acc,
                                                 const float* part_ml, int n_q_heads,
-                                                int head_dim, int n_splits, float sink_log2) {
+                                                int head_dim, int n_splits, float sink_log2,
+                                                const float* __restrict__ sinks) {
+  if (sinks != nullptr) sink_log2 = sinks[blockIdx.y] * 1.4426950408889634f;
   pdl_launch_dependents();
   pdl_wait();
   const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
@@ -276,7 +279,7 @@ template <int DCH>
 static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                       const int* token_slot, PagedKV cache, int n_tokens, int n_q_heads,
                       float scale, int window, int n_splits, int keys_per_split, float* part_acc,
-                      float* part_ml, float sink, cudaStream_t stream) {
+                      float* part_ml, float sink, const float* sinks, cudaStream_t stream) {
   constexpr int D = DCH * 32;
   const int group = n_q_heads / cache.heads;
   const int row_blocks = (group + 15) / 16;
@@ -295,12 +298,12 @@ static int launch_dch(bf16* out, const bf16* q, int q_row_stride, const int* pos
   cudaError_t e = launch_pdl(attention_decode_bf16_kernel<DCH>, grid, dim3(kDecWarps * 32), smem,
                              stream, out, q, q_row_stride, positions, token_slot, cache, n_q_heads,
                              row_blocks, scale * 1.4426950408889634f, window, n_splits,
-                             keys_per_split, part_acc, part_ml, sink * 1.4426950408889634f);
+                             keys_per_split, part_acc, part_ml, sink * 1.4426950408889634f, sinks);
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
   return (int)launch_pdl(attention_decode_combine_kernel, cgrid, dim3(64), 0, stream, out,
                          (const float*)part_acc, (const float*)part_ml, n_q_heads, D, n_splits,
-                         sink * 1.4426950408889634f);
+                         sink * 1.4426950408889634f, sinks);
 }
 
 }  // namespace ek
@@ -315,7 +318,7 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
                                        int n_q_heads, int n_kv_heads, int head_dim, float scale,
                                        int window, int n_splits, int keys_per_split,
                                        float* part_acc, float* part_ml, float sink,
-                                       cudaStream_t stream) {
+                                       const float* sinks, cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0) return 0;
   if (head_dim % 32 || head_dim < 32 || head_dim > 256 || n_kv_heads <= 0 ||
@@ -327,7 +330,7 @@ EK_EXPORT int ek_attention_decode_bf16(void* out, const void* q, int q_row_strid
   case DCH:                                                                                       \
     return launch_dch<DCH>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot, cache, \
                            n_tokens, n_q_heads, scale, window, n_splits, keys_per_split, part_acc, \
-                           part_ml, sink, stream);
+                           part_ml, sink, sinks, stream);
   switch (head_dim / 32) {
     EK_CASE(1) EK_CASE(2) EK_CASE(3) EK_CASE(4) EK_CASE(5) EK_CASE(6) EK_CASE(7) EK_CASE(8)
   }
@@ -399,5 +402,5 @@ EK_EXPORT int ek_attention_decode_bf16_noalloc(void* out, const void* q, int q_r
   return ek_attention_decode_bf16(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,
                                   block_table, table_stride, n_tokens, n_q_heads, n_kv_heads,
                                   head_dim, scale, window, n_splits, keys_per_split, part_acc,
-                                  part_ml, -INFINITY, stream);
+                                  part_ml, -INFINITY, nullptr, stream);
 }

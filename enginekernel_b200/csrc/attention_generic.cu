@@ -5,6 +5,7 @@
 // with a running maximum and sum (online softmax) so that no score row is stored.
 // An optional sink - a key without a value whose fixed score `sink` every query sees - adds
 // exp(sink) to the softmax denominator once per (token, head); -INFINITY switches it off.
+// `sinks`, if given, holds one such score per query head and takes the place of `sink`.
 // It serves whole prompts, chunks and single decoded tokens alike, since each token
 // carries its own position and slot; the faster bfloat16 kernels in attention_bf16.cu
 // cover the common head sizes, this one covers everything and is the 32-bit path.
@@ -65,7 +66,8 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          const int* __restrict__ token_slot, PagedKV cache,
                                          int n_q_heads, float scale, int window, int n_splits,
                                          int keys_per_split, float* __restrict__ part_acc,
-                                         float* __restrict__ part_ml, float sink) {
+                                         float* __restrict__ part_ml, float sink,
+                                         const float* __restrict__ sinks) {
   __shared__ float q_s[EK_MAX_HEAD_DIM];
   __shared__ float p_s[kAttnThreads];
   __shared__ size_t voff_s[kAttnThreads];
@@ -73,6 +75,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 
   const int t = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x;
+  if (sinks != nullptr) sink = sinks[h];        // a sink score of its own for every query head
   const int d = cache.head_dim;
   const int kv_head = h / (n_q_heads / cache.heads);
   const int pos = positions[t];
@@ -147,7 +150,9 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
 template <typename T>
 __global__ void attention_combine_kernel(T* __restrict__ out, const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml, int n_q_heads,
-                                         int head_dim, int n_splits, float sink) {
+                                         int head_dim, int n_splits, float sink,
+                                         const float* __restrict__ sinks) {
+  if (sinks != nullptr) sink = sinks[blockIdx.y];
   const size_t th = (size_t)blockIdx.x * n_q_heads + blockIdx.y;
   const float* ml = part_ml + 2 * th * n_splits;
   float m = -INFINITY;
@@ -171,7 +176,7 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
                   const int* block_table, int table_stride, int n_tokens, int n_q_heads,
                   int n_kv_heads, int head_dim, float scale, int window, int n_splits,
                   int keys_per_split, float* part_acc, float* part_ml, float sink,
-                  cudaStream_t stream) {
+                  const float* sinks, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || n_kv_heads <= 0 ||
       n_q_heads % n_kv_heads || n_q_heads > 65535 || n_splits < 1 || n_splits > 65535 ||
@@ -181,12 +186,12 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
   dim3 grid(n_tokens, n_q_heads, n_splits);
   attention_generic_kernel<T><<<grid, kAttnThreads, 0, stream>>>(
       (T*)out, (const T*)q, q_row_stride, positions, token_slot, cache, n_q_heads, scale, window,
-      n_splits, keys_per_split, part_acc, part_ml, sink);
+      n_splits, keys_per_split, part_acc, part_ml, sink, sinks);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || n_splits == 1) return (int)e;
   dim3 cgrid(n_tokens, n_q_heads);
   attention_combine_kernel<T><<<cgrid, 64, 0, stream>>>((T*)out, part_acc, part_ml, n_q_heads,
-                                                        head_dim, n_splits, sink);
+                                                        head_dim, n_splits, sink, sinks);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -198,11 +203,11 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
       const void* k_pages, const void* v_pages, const int* block_table, int table_stride,      \
       int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, float scale, int window,      \
       int n_splits, int keys_per_split, float* part_acc, float* part_ml, float sink,           \
-      cudaStream_t stream) {                                                                   \
+      const float* sinks, cudaStream_t stream) {                                                                   \
     return ek::launch<T>(out, q, q_row_stride, positions, token_slot, k_pages, v_pages,        \
                          block_table, table_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, \
                          scale, window, n_splits, keys_per_split, part_acc, part_ml, sink,     \
-                         stream);                                                              \
+                         sinks, stream);                                                              \
   }
 
 EK_INSTANTIATE(f32, float)

@@ -59,7 +59,7 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
                               const int* __restrict__ positions, const int* __restrict__ token_slot,
                               const int* __restrict__ cu_seqlens, int n_seqs, PagedKV cache,
                               int n_q_heads, float scale_log2, int window, int tok_per_tile,
-                              float sink_log2) {
+                              float sink_log2, const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int tile_info[3];                 // first token (packed index), tokens, sequence
   const int D = cache.head_dim;
@@ -256,7 +256,15 @@ attention_prefill_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ q
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
   // a sink: one more term exp(sink) in the denominator, with no value (sink_log2 = -inf: none)
-  if (sink_log2 > -INFINITY) {
+  // (`sinks`: one score per query head instead of the same for all)
+  if (sinks != nullptr) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = r == 0 ? row_lo : row_hi;
+      if (row < n_rows && l_run[r] > 0.f)
+        l_run[r] += exp2f(sinks[kv_head * group + row % group] * 1.4426950408889634f - m_run[r]);
+    }
+  } else if (sink_log2 > -INFINITY) {
 #pragma unroll
     for (int r = 0; r < 2; ++r)
       if (l_run[r] > 0.f) l_run[r] += exp2f(sink_log2 - m_run[r]);
@@ -285,7 +293,7 @@ template <int DMAX>
 static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* positions,
                        const int* token_slot, const int* cu_seqlens, int n_seqs, int n_tokens,
                        PagedKV cache, int n_q_heads, float scale, int window, float sink,
-                       cudaStream_t stream) {
+                       const float* sinks, cudaStream_t stream) {
   const int group = n_q_heads / cache.heads;
   const int tok_per_tile = kPfRows / group;
   const int D = cache.head_dim, LD = D + 8;
@@ -299,7 +307,7 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
   if (tiles > 65535) return EK_ERR_ARG;
   attention_prefill_bf16_kernel<DMAX><<<grid, kPfWarps * 32, smem, stream>>>(
       out, q, q_row_stride, positions, token_slot, cu_seqlens, n_seqs, cache, n_q_heads,
-      scale * 1.4426950408889634f, window, tok_per_tile, sink * 1.4426950408889634f);
+      scale * 1.4426950408889634f, window, tok_per_tile, sink * 1.4426950408889634f, sinks);
   EK_RETURN_LAUNCH_STATUS();
 }
 
@@ -308,14 +316,15 @@ static int launch_dmax(bf16* out, const bf16* q, int q_row_stride, const int* po
 // head_dim a multiple of 16 up to 256; the group (query heads per KV head) at most 128.
 // Tokens of a sequence must stand at consecutive positions in the step.
 // `sink`: score of a key without a value that every query also sees (its exponential is one more
-// term of the softmax denominator); -INFINITY for none.
+// term of the softmax denominator); -INFINITY for none.  `sinks` (may be null): one such score per
+// query head, in place of `sink`.
 EK_EXPORT int ek_attention_prefill_bf16(void* out, const void* q, int q_row_stride,
                                         const int* positions, const int* token_slot,
                                         const int* cu_seqlens, int n_seqs, int n_tokens,
                                         const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_stride, int n_q_heads,
                                         int n_kv_heads, int head_dim, float scale, int window,
-                                        float sink, cudaStream_t stream) {
+                                        float sink, const float* sinks, cudaStream_t stream) {
   using namespace ek;
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 ||
@@ -324,10 +333,10 @@ EK_EXPORT int ek_attention_prefill_bf16(void* out, const void* q, int q_row_stri
   PagedKV cache{(void*)k_pages, (void*)v_pages, block_table, table_stride, n_kv_heads, head_dim};
   if (head_dim <= 64)
     return launch_dmax<64>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,
-                           cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, stream);
+                           cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks, stream);
   if (head_dim <= 128)
     return launch_dmax<128>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,
-                            cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, stream);
+                            cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks, stream);
   return launch_dmax<256>((bf16*)out, (const bf16*)q, q_row_stride, positions, token_slot,
-                          cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, stream);
+                          cu_seqlens, n_seqs, n_tokens, cache, n_q_heads, scale, window, sink, sinks, stream);
 }

@@ -1,0 +1,303 @@
+// Routed experts: a router that picks `top` of E small feed-forwards per token, and the experts'
+// products for the tokens that chose them.
+//
+//   route     scores = softmax(logits) over all experts (32-bit); experts form `n_groups` equal
+//             groups of neighbours, a group's score is its best expert's, only experts of the
+//             `keep` best groups can be chosen; the `top` largest of those; weights = chosen
+//             scores / (their sum + 1e-20) * scale.  A warp a token.
+//   plan      the (token, choice) pairs sorted by expert, and the row tiles of every expert's
+//             stretch, made on the device: the host never sees who chose what.
+//   expert product  out[row] = f(x[row] . W_e^T) over the tiles of the plan, FFMA with 32-bit
+//             sums in ascending k, so a pair's result does not depend on its neighbours; the up
+//             form gathers its rows by token and applies the activation, the down form scales by
+//             the pair's weight and scatters 32-bit rows by pair.
+//   combine   out[t] = sum over the token's choices, in the order they were chosen.
+#include "common.cuh"
+
+namespace ek {
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+constexpr int kRouteWarps = 4;
+
+// logits [T, E] 32-bit -> sel_expert [T, top] int32, sel_weight [T, top] 32-bit.
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(int* __restrict__ sel_expert, float* __restrict__ sel_weight,
+                 const float* __restrict__ logits, int n_tokens, int E, int n_groups, int keep, int top,
+                 float scale) {
+  extern __shared__ float route_s[];            // per warp: scores [E], candidates [E], groups [n_groups]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= n_tokens) return;
+  float* s = route_s + (size_t)warp * (2 * E + n_groups);
+  float* cand = s + E;
+  float* gs = cand + E;
+  const float* z = logits + (size_t)t * E;
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) { const float x = expf(z[e] - m); s[e] = x; sum += x; }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < E; e += 32) { s[e] *= inv; cand[e] = s[e]; }
+  __syncwarp();
+  if (n_groups > 1 && keep < n_groups) {
+    const int per = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float best = -1.f;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, s[e]);
+      gs[g] = best;
+    }
+    __syncwarp();
+    for (int round = 0; round < keep; ++round) {
+      float bv = -2.f; int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32)
+        if (gs[g] > bv) { bv = gs[g]; bi = g; }
+      warp_argmax(bv, bi);
+      if (lane == 0) gs[bi] = -3.f;             // kept
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / per] != -3.f) cand[e] = -1.f;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float bv = -2.f; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (cand[e] > bv) { bv = cand[e]; bi = e; }
+    warp_argmax(bv, bi);
+    const float sc = s[bi];
+    total += sc;
+    if (lane == 0) {
+      sel_expert[(size_t)t * top + k] = bi;
+      sel_weight[(size_t)t * top + k] = sc;     // scaled below
+      cand[bi] = -2.f;
+    }
+    __syncwarp();
+  }
+  const float f = scale / (total + 1e-20f);
+  for (int k = lane; k < top; k += 32) sel_weight[(size_t)t * top + k] *= f;
+}
+
+constexpr int kTileRows = 32;
+
+// One block.  sel_expert [P] -> sorted_pair [P] (pairs grouped by expert), tiles [max_tiles][3] =
+// (expert, first sorted row, rows), n_tiles[0].
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(int* __restrict__ sorted_pair, int* __restrict__ tiles, int* __restrict__ n_tiles,
+                const int* __restrict__ sel_expert, int P, int E) {
+  extern __shared__ int plan_s[];               // counts [E], first row [E], first tile [E + 1]
+  pdl_launch_dependents();
+  pdl_wait();
+  int* counts = plan_s;
+  int* first = counts + E;
+  int* tile0 = first + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = sel_expert[p];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int row = 0, tile = 0;
+    for (int e = 0; e < E; ++e) {
+      first[e] = row;
+      tile0[e] = tile;
+      row += counts[e];
+      tile += (counts[e] + kTileRows - 1) / kTileRows;
+    }
+    tile0[E] = tile;
+    n_tiles[0] = tile;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int n = counts[e];
+    for (int i = 0, tile = tile0[e]; i < n; i += kTileRows, ++tile) {
+      tiles[3 * tile] = e;
+      tiles[3 * tile + 1] = first[e] + i;
+      tiles[3 * tile + 2] = min(kTileRows, n - i);
+    }
+    counts[e] = first[e];                       // from here on: the next free row of the expert
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = sel_expert[p];
+    if (e >= 0 && e < E) sorted_pair[atomicAdd(&counts[e], 1)] = p;
+  }
+}
+
+constexpr int ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3;
+
+__device__ __forceinline__ float activate(float z, int act) {
+  if (act == ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (act == ACT_SILU) return z / (1.f + expf(-z));
+  if (act == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+
+// grid (max tiles, column tiles).  UP: a[row] = x[pair / top], out T [sorted row][N] = act(.).
+// DOWN: a[row] = in[sorted row], out 32-bit [pair][N] = weight[pair] * (.).
+template <typename T, bool UP>
+__global__ void __launch_bounds__(256)
+moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, const T* __restrict__ w,
+                          const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                          const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
+                          int top, int N, int K, int act) {
+  constexpr int BM = kTileRows, BN = 64, BK = 16, TM = 2, TN = 4, PAD = 4;
+  __shared__ __align__(16) float As[BK][BM + PAD];
+  __shared__ __align__(16) float Ws[BK][BN + PAD];
+  __shared__ int src_row[BM];
+  __shared__ int pair_s[BM];
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.x >= n_tiles[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int tid = threadIdx.x;
+  if (tid < BM) {
+    const int p = tid < rows ? sorted_pair[row0 + tid] : -1;
+    pair_s[tid] = p;
+    src_row[tid] = p < 0 ? -1 : (UP ? p / top : row0 + tid);
+  }
+  __syncthreads();
+  const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+  const int n0 = blockIdx.y * BN;
+  const T* we = w + (size_t)e * N * K;
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int idx = tid; idx < BM * BK; idx += 256) {
+      const int row = idx / BK, kk = idx % BK;
+      const int src = src_row[row], gk = k0 + kk;
+      As[kk][row] = (src >= 0 && gk < K) ? to_f<T>(a[(size_t)src * K + gk]) : 0.f;
+    }
+    for (int idx = tid; idx < BN * BK; idx += 256) {
+      const int row = idx / BK, kk = idx % BK;
+      const int gn = n0 + row, gk = k0 + kk;
+      Ws[kk][row] = (gn < N && gk < K) ? to_f<T>(we[(size_t)gn * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[TM], bv[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) av[i] = As[kk][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) bv[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = ty * TM + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int gn = n0 + tx * TN + j;
+      if (gn >= N) continue;
+      if (UP) {
+        ((T*)out_)[(size_t)(row0 + r) * N + gn] = from_f<T>(activate(acc[i][j], act));
+      } else {
+        const int p = pair_s[r];
+        ((float*)out_)[(size_t)p * N + gn] = acc[i][j] * pair_weight[p];
+      }
+    }
+  }
+}
+
+// out[t, :] = sum_k pair_out[t * top + k, :], k ascending.
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ pair_out, int top,
+                                   int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a += pair_out[(t * top + k) * width + i];
+    out[t * width + i] = from_f<T>(a);
+  }
+}
+
+}  // namespace ek
+
+EK_EXPORT int ek_moe_tile_rows() { return ek::kTileRows; }
+
+EK_EXPORT int ek_moe_route(int* sel_expert, float* sel_weight, const float* logits, int n_tokens, int E,
+                           int n_groups, int keep, int top, float scale, cudaStream_t stream) {
+  using namespace ek;
+  if (n_tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || n_groups < 1 || E % n_groups || keep < 1 || keep > n_groups ||
+      top > keep * (E / n_groups))
+    return EK_ERR_ARG;
+  const size_t smem = (size_t)kRouteWarps * (2 * E + n_groups) * sizeof(float);
+  if (smem > 200 * 1024) return EK_ERR_ARG;
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  moe_route_kernel<<<(n_tokens + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, stream>>>(
+      sel_expert, sel_weight, logits, n_tokens, E, n_groups, keep, top, scale);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+EK_EXPORT int ek_moe_plan(int* sorted_pair, int* tiles, int* n_tiles, const int* sel_expert, int P, int E,
+                          cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > 8192) return EK_ERR_ARG;
+  ek::moe_plan_kernel<<<1, 1024, (size_t)(3 * E + 1) * sizeof(int), stream>>>(sorted_pair, tiles, n_tiles,
+                                                                             sel_expert, P, E);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+#define EK_INSTANTIATE(SUFFIX, T)                                                                     \
+  EK_EXPORT int ek_moe_expert_up_##SUFFIX(void* out, const void* x, const void* w, const int* tiles,  \
+                                          const int* n_tiles, const int* sorted_pair, int max_tiles,  \
+                                          int top, int N, int K, int act, cudaStream_t stream) {      \
+    using namespace ek;                                                                               \
+    if (max_tiles <= 0) return 0;                                                                     \
+    if (N <= 0 || K <= 0 || top <= 0 || (N + 63) / 64 > 65535) return EK_ERR_ARG;                     \
+    dim3 grid(max_tiles, (N + 63) / 64);                                                              \
+    moe_expert_product_kernel<T, true><<<grid, 256, 0, stream>>>(                                     \
+        out, (const T*)x, (const T*)w, tiles, n_tiles, sorted_pair, nullptr, top, N, K, act);         \
+    EK_RETURN_LAUNCH_STATUS();                                                                        \
+  }                                                                                                   \
+  EK_EXPORT int ek_moe_expert_down_##SUFFIX(float* out, const void* a, const void* w, const int* tiles, \
+                                            const int* n_tiles, const int* sorted_pair,               \
+                                            const float* pair_weight, int max_tiles, int N, int K,    \
+                                            cudaStream_t stream) {                                    \
+    using namespace ek;                                                                               \
+    if (max_tiles <= 0) return 0;                                                                     \
+    if (N <= 0 || K <= 0 || (N + 63) / 64 > 65535) return EK_ERR_ARG;                                 \
+    dim3 grid(max_tiles, (N + 63) / 64);                                                              \
+    moe_expert_product_kernel<T, false><<<grid, 256, 0, stream>>>(                                    \
+        out, (const T*)a, (const T*)w, tiles, n_tiles, sorted_pair, pair_weight, 1, N, K, 0);         \
+    EK_RETURN_LAUNCH_STATUS();                                                                        \
+  }                                                                                                   \
+  EK_EXPORT int ek_moe_combine_##SUFFIX(void* out, const float* pair_out, int n_tokens, int top,      \
+                                        int width, cudaStream_t stream) {                             \
+    if (n_tokens <= 0) return 0;                                                                      \
+    ek::moe_combine_kernel<T><<<n_tokens, 256, 0, stream>>>((T*)out, pair_out, top, width);           \
+    EK_RETURN_LAUNCH_STATUS();                                                                        \
+  }
+
+EK_INSTANTIATE(f32, float)
+EK_INSTANTIATE(bf16, ek::bf16)

@@ -45,6 +45,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
         for norm in layer.norms.values():
             for ts in _part_tensors("norm", norm):
                 out[ts.name] = ts
+        for ts in _part_tensors("block", layer.block):       # an arrangement may hold tensors of its own
+            out[ts.name] = ts
     return out
 
 
@@ -87,6 +89,7 @@ class DecoderModel:
             self.position_table = tensors[s.position_table.name].to(self.dtype).contiguous()
         self.final_norm.load(tensors)
         for block in self.blocks:
+            block.load(tensors)
             block.mixer.load(tensors)
             if block.feed_forward is not None:
                 block.feed_forward.load(tensors)
@@ -123,7 +126,7 @@ class DecoderModel:
         total += self.final_norm.bytes_read_per_step(n_tokens)
         for run in self.spec.schedule:
             b = self.blocks[run.layer]
-            for part in (b.mixer, b.feed_forward, *b.norms.values()):
+            for part in (b, b.mixer, b.feed_forward, *b.norms.values()):
                 if part is not None:
                     total += part.bytes_read_per_step(n_tokens)
         return total
@@ -140,6 +143,7 @@ class DecoderModel:
                       pos_table=self.position_table, positions=ctx.positions)
         pending = None
         schedule = self.spec.schedule
+        stream = self.blocks[schedule[0].layer].open_stream(stream, ctx)
         for i, run in enumerate(schedule):
             block = self.blocks[run.layer]
             if run.add_embedding:
@@ -159,7 +163,7 @@ class DecoderModel:
                 pending = block.forward(stream, pending, ctx, entry, run.writes_cache, next_norm=next_norm)
             else:
                 pending = block.forward(stream, pending, ctx, entry, run.writes_cache)
-        return stream, pending
+        return self.blocks[schedule[-1].layer].collapse(stream, pending, ctx)
 
     def logits(self, ctx: StepContext, stream, pending, rows, n_rows: int):
         """32-bit logits [n_rows, vocab] at the stream rows ``rows`` (int32, on device)."""

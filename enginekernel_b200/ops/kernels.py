@@ -258,7 +258,7 @@ def qk_norm_rope_kv(qkv, n_tokens, q_gain, k_gain, cos, sin, rot_dim, positions,
 # ------------------------------------------------------------------ attention
 _attn_generic = _per_dtype("attention_generic", "ek_attention_generic",
                            [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_int, _P, _P, c_float, _P])
+                            c_float, c_int, c_int, c_int, _P, _P, c_float, _P, _P])
 _NO_SINK = float("-inf")
 
 
@@ -267,12 +267,23 @@ def _sink(sink) -> float:
     return _NO_SINK if sink is None else float(sink)
 
 
+def _sinks(sinks, n_q_heads):
+    """One sink score per query head (32-bit, on the device), or None."""
+    if sinks is None:
+        return None
+    _need_cuda(sinks)
+    _need(sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_q_heads,
+          "attention: per-head sinks are 32-bit, one per query head")
+    return sinks.data_ptr()
+
+
 def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
                       n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
-                      keys_per_split=0, part_acc=None, part_ml=None, sink=None):
+                      keys_per_split=0, part_acc=None, part_ml=None, sink=None, sinks=None):
     """out[t, h*D:(h+1)*D] = softmax(scale q.K^T) V over the keys token t may see.  ``sink``: the
     score of one more key without a value that every query sees - exp(sink) is added to the
-    softmax denominator (the same in every attention kernel below).
+    softmax denominator (the same in every attention kernel below).  ``sinks`` [NQ] (32-bit):
+    one such score per query head instead (here and in the two mma.sync kernels).
 
     ``q`` is any tensor whose row t starts with the NQ*D query values (the fused q/k/v
     rows qualify).  With ``n_splits`` > 1 the keys are cut every ``keys_per_split`` and
@@ -292,14 +303,14 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
                            _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                            n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale),
                            int(window or 0), n_splits, keys_per_split, _ptr(part_acc),
-                           _ptr(part_ml), _sink(sink), _stream())
+                           _ptr(part_ml), _sink(sink), _sinks(sinks, n_q_heads), _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
 
 
 _attn_decode_bf16 = Function("attention_decode_bf16", "ek_attention_decode_bf16",
                              [_P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_int, c_int, c_int, _P, _P, c_float, _P])
+                              c_float, c_int, c_int, c_int, _P, _P, c_float, _P, _P])
 
 
 def attention_decode_supported(dtype, head_dim):
@@ -308,7 +319,7 @@ def attention_decode_supported(dtype, head_dim):
 
 def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pages, block_table,
                           n_q_heads, n_kv_heads, head_dim, scale, window=None, n_splits=1,
-                          keys_per_split=0, part_acc=None, part_ml=None, sink=None):
+                          keys_per_split=0, part_acc=None, part_ml=None, sink=None, sinks=None):
     """One query token per row of ``q`` (bfloat16, head_dim a multiple of 32): same contract
     as :func:`attention_generic`; ``keys_per_split`` must be a multiple of 16, or 0 to cut
     every token's own visible keys into ``n_splits`` equal parts."""
@@ -327,7 +338,8 @@ def attention_decode_bf16(out, q, n_tokens, positions, token_slot, k_pages, v_pa
     _attn_decode_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                       _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.stride(0),
                       n_tokens, n_q_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
-                      n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _sink(sink), _stream())
+                      n_splits, keys_per_split, _ptr(part_acc), _ptr(part_ml), _sink(sink),
+                      _sinks(sinks, n_q_heads), _stream())
     if n_splits > 1:
         count_extra_launches()               # the merge kernel
 
@@ -388,7 +400,7 @@ def attention_decode_tma(out, q, n_tokens, positions, token_slot, k_pages, v_pag
 
 _attn_prefill_bf16 = Function("attention_prefill_bf16", "ek_attention_prefill_bf16",
                               [_P, _P, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int,
-                               c_int, c_int, c_float, c_int, c_float, _P])
+                               c_int, c_int, c_float, c_int, c_float, _P, _P])
 
 
 def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
@@ -398,7 +410,7 @@ def attention_prefill_supported(dtype, head_dim, n_q_heads, n_kv_heads):
 
 def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, n_seqs, k_pages,
                            v_pages, block_table, n_q_heads, n_kv_heads, head_dim, scale,
-                           window=None, sink=None):
+                           window=None, sink=None, sinks=None):
     """Several new tokens per sequence (bfloat16): sequence b owns rows cu_seqlens[b] ..
     cu_seqlens[b+1] of ``q``, which stand at consecutive positions; their keys and values
     are already in the pages."""
@@ -413,7 +425,7 @@ def attention_prefill_bf16(out, q, n_tokens, positions, token_slot, cu_seqlens, 
     _attn_prefill_bf16(_ptr(out), _ptr(q), q.stride(0), _ptr(positions), _ptr(token_slot),
                        _ptr(cu_seqlens), n_seqs, n_tokens, _ptr(k_pages), _ptr(v_pages),
                        _ptr(block_table), block_table.stride(0), n_q_heads, n_kv_heads, head_dim,
-                       float(scale), int(window or 0), _sink(sink), _stream())
+                       float(scale), int(window or 0), _sink(sink), _sinks(sinks, n_q_heads), _stream())
 
 
 _attn_prefill_tc = Function("attention_prefill_tc", "ek_attention_prefill_tc",
@@ -943,6 +955,237 @@ def decode_advance(sampled, token_ids, positions, draws, remaining, out_tokens, 
     _decode_advance(_ptr(sampled), _ptr(token_ids), _ptr(positions), _ptr(draws), _ptr(remaining),
                     _ptr(out_tokens), _ptr(step_index), _ptr(stop_ids), n_stop, batch,
                     out_tokens.shape[0], _stream())
+
+
+# ------------------------------------------------------------------ several residual streams
+_hc_broadcast = Function("hyper", "ek_hc_broadcast", [_P, _P, c_int, c_int, c_int, _P])
+_hc_step = _per_dtype("hyper", "ek_hc_step", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
+MAX_RESIDUAL_STREAMS = 8
+
+
+def hc_broadcast(streams, x, n_tokens):
+    """streams[t, s, :] = x[t, :] for every stream s (32-bit)."""
+    _need_cuda(streams, x)
+    _need(streams.dtype == x.dtype == torch.float32 and streams.is_contiguous() and x.is_contiguous()
+          and streams.dim() == 3 and streams.shape[-1] == x.shape[-1], "hc_broadcast: streams [T, n, W], x [T, W], 32-bit")
+    n, width = streams.shape[1], streams.shape[2]
+    if lib.recording():
+        lib.annotate(bytes=4 * n_tokens * width * (n + 1))
+    _hc_broadcast(_ptr(streams), _ptr(x), n_tokens, n, width, _stream())
+
+
+def hc_step(streams, n_tokens, y=None, write_mix=None, write_out=None, read_in=None, u=None):
+    """With ``y`` [T, W]: x_t <- sum_s write_mix[s, t] x_s + write_out[t] y for all streams at once, in
+    place.  Then, with ``u`` [T, W] (32-bit): u = sum_s read_in[s] x_s (``read_in`` None: the plain
+    sum).  Coefficients are 32-bit device tensors."""
+    _need_cuda(streams, y, write_mix, write_out, read_in, u)
+    _need(streams.dtype == torch.float32 and streams.is_contiguous() and streams.dim() == 3,
+          "hc_step: streams [T, n, W] in 32-bit")
+    n, width = streams.shape[1], streams.shape[2]
+    _need(n <= MAX_RESIDUAL_STREAMS, f"hc_step: at most {MAX_RESIDUAL_STREAMS} residual streams")
+    for c, size in ((write_mix, n * n), (write_out, n), (read_in, n)):
+        _need(c is None or (c.dtype == torch.float32 and c.is_contiguous() and c.numel() == size),
+              "hc_step: 32-bit coefficients [n], [n], [n, n]")
+    _need(y is None or (y.is_contiguous() and y.shape[-1] == width and write_mix is not None
+                        and write_out is not None), "hc_step: y [T, W] with its coefficients")
+    _need(u is None or (u.dtype == torch.float32 and u.is_contiguous() and u.shape[-1] == width),
+          "hc_step: u [T, W] in 32-bit")
+    dtype = y.dtype if y is not None else torch.float32
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * width * (4 * n * (2 if y is not None else 1)
+                                               + (y.element_size() if y is not None else 0)
+                                               + (4 if u is not None else 0)))
+    _hc_step[dtype](_ptr(streams), _ptr(y), _ptr(write_mix), _ptr(write_out), _ptr(read_in), _ptr(u),
+                    n_tokens, n, width, _stream())
+
+
+# ------------------------------------------------------------------ latent attention
+_latent_prepare = _per_dtype("latent", "ek_latent_prepare",
+                             [_P, _P, c_int, _P, _P, c_float, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int,
+                              c_int, c_int, c_int, c_int, c_int, _P])
+_head_linear = _per_dtype("latent", "ek_head_linear",
+                          [_P, c_int, c_int, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                           _P, _P, _P, _P])
+
+
+def latent_prepare(cq, proj, n_tokens, gain_q, gain_kv, eps, cos, sin, rot_dims, positions, token_slot,
+                   pages, block_table, q_rank, kv_rank, rot_dim, write_cache=True):
+    """``proj`` [T, q_rank + kv_rank + rot_dim] (32-bit): cq = gain_q * rms-normed first part (activation
+    type); the token's cache row (``pages`` [page, 1, PAGE, D], D >= kv_rank + rot_dim) becomes
+    [gain_kv * rms-normed latent | rotated key part | zeros]."""
+    _need_cuda(cq, proj, gain_q, gain_kv, cos, sin, positions, token_slot, pages, block_table)
+    _need(proj.dtype == torch.float32 and proj.stride(-1) == 1, "latent_prepare: 32-bit projections")
+    _need(cq.dtype == pages.dtype and cq.is_contiguous() and cq.shape[-1] == q_rank, "latent_prepare: cq [T, q_rank]")
+    _need(pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == 1 and pages.shape[2] == PAGE,
+          "latent_prepare: pages [page, 1, PAGE, D]")
+    _need(gain_q.dtype == gain_kv.dtype == torch.float32 and gain_q.numel() == q_rank
+          and gain_kv.numel() == kv_rank, "latent_prepare: 32-bit gains")
+    _need(rot_dims == 0 or (cos.dtype == torch.float32 and cos.shape[-1] == rot_dims // 2 and cos.is_contiguous()
+                            and sin.is_contiguous()), "latent_prepare: cos/sin [positions, rot_dims / 2]")
+    d = pages.shape[-1]
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * (4 * (q_rank + kv_rank + rot_dim) + cq.element_size() * (q_rank + d)))
+    _latent_prepare[cq.dtype](_ptr(cq), _ptr(proj), proj.stride(0), _ptr(gain_q), _ptr(gain_kv), float(eps),
+                              _ptr(cos), _ptr(sin), rot_dims, _ptr(positions), _ptr(token_slot), _ptr(pages),
+                              _ptr(block_table), block_table.stride(0), n_tokens, q_rank, kv_rank, rot_dim, d,
+                              1 if write_cache else 0, _stream())
+
+
+def head_linear(out, x, w, n_tokens, heads, n_in, n_out, rot=None):
+    """out[t, h, :n_out] = w[h]^T-applied x[t, h, :n_in] for every head: ``w`` is [heads, n_in, n_out],
+    ``x`` [T, heads, >= n_in] and ``out`` [T, heads, >= n_out] (any row and head strides, dense
+    values).  ``rot=(rot_dim, rot_dims, cos, sin, positions)``: the ``rot_dim`` values behind the
+    ``n_in`` of a head are rotated (the first ``rot_dims`` of them, NeoX pairing) and written behind the
+    ``n_out`` results, zeros up to the head's stride."""
+    _need_cuda(out, x, w)
+    _need(out.dtype == x.dtype == w.dtype, "head_linear: one dtype")
+    _need(out.dim() == 3 and x.dim() == 3 and out.stride(-1) == 1 and x.stride(-1) == 1 and w.is_contiguous()
+          and tuple(w.shape) == (heads, n_in, n_out), "head_linear: x, out [T, heads, .], w [heads, n_in, n_out]")
+    r, rot_dims, cos, sin, positions = 0, -1, None, None, None
+    if rot is not None:
+        r, rot_dims, cos, sin, positions = rot
+        _need_cuda(cos, sin, positions)
+        _need(x.shape[-1] >= n_in + r and out.stride(1) >= n_out + r, "head_linear: room for the rotated tail")
+    if lib.recording():
+        lib.annotate(bytes=x.element_size() * (heads * n_in * n_out + n_tokens * heads * (n_in + n_out + 2 * r)),
+                     flops=2 * n_tokens * heads * n_in * n_out)
+    _head_linear[x.dtype](_ptr(out), out.stride(0), out.stride(1), _ptr(x), x.stride(0), x.stride(1), _ptr(w),
+                          n_tokens, heads, n_in, n_out, r, rot_dims, _ptr(cos), _ptr(sin), _ptr(positions),
+                          _stream())
+
+
+# ------------------------------------------------------------------ delta rule with a decay per key channel
+_delta_state_rows = Function("delta", "ek_delta_state_rows", [c_int], check_status=False)
+_delta_prepare = Function("delta", "ek_delta_prepare",
+                          [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, c_longlong, c_longlong, _P, _P,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P])
+_delta_conv_tail = Function("delta", "ek_delta_conv_tail",
+                            [_P, c_longlong, c_longlong, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
+_delta_scan = Function("delta", "ek_delta_scan",
+                       [_P, _P, _P, _P, _P, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+_delta_out_norm = _per_dtype("delta", "ek_delta_out_norm",
+                             [_P, _P, _P, c_int, _P, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_int, _P])
+DELTA_MAX_KEY_DIM = 256
+
+
+def delta_state_rows(dim: int) -> int:
+    """Rows of S per column that the scan keeps for keys of ``dim`` values (``dim`` rounded up to 32,
+    64, 128 or 256)."""
+    if not 0 < dim <= DELTA_MAX_KEY_DIM:
+        raise KernelError(f"the delta-rule scan takes key sizes up to {DELTA_MAX_KEY_DIM}, not {dim}")
+    for rows in (32, 64, 128, 256):
+        if dim <= rows:
+            return rows
+
+
+def delta_prepare(qn, kn, vc, beta, decay, proj, n_tokens, conv_w, a2t, dt_bias, a_log, state, tail_offset,
+                  positions, token_slot, shape):
+    """``shape`` = (heads, kv_heads, dim, vdim, taps, rank_a, rank_g).  ``proj`` [T, q|k|v|beta|a1|g1] in
+    32-bit; ``state`` [slots, values] 32-bit with the convolution's last inputs from ``tail_offset`` on.
+    Writes the unit q and k, the convolved v, beta and the decays (all 32-bit)."""
+    _need_cuda(qn, kn, vc, beta, decay, proj, conv_w, a2t, dt_bias, a_log, state, positions, token_slot)
+    for t in (qn, kn, vc, beta, decay, proj, conv_w, a2t, dt_bias, a_log, state):
+        _need(t.dtype == torch.float32 and t.stride(-1) == 1, "delta_prepare: 32-bit tensors")
+    if lib.recording():
+        lib.annotate(bytes=4 * n_tokens * (proj.shape[-1] + 2 * qn.shape[-1] + vc.shape[-1] + decay.shape[-1]))
+    _delta_prepare(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay), _ptr(proj), proj.stride(0),
+                   _ptr(conv_w), _ptr(a2t), _ptr(dt_bias), _ptr(a_log), _ptr(state), state.stride(0),
+                   tail_offset, _ptr(positions), _ptr(token_slot), n_tokens, *[int(v) for v in shape], _stream())
+
+
+def delta_conv_tail(state, tail_offset, proj, cu_seqlens, positions, token_slot, n_seqs, channels, taps):
+    """The last ``taps - 1`` convolution inputs of every sequence of the step go to its state."""
+    _need_cuda(state, proj, cu_seqlens, positions, token_slot)
+    _delta_conv_tail(_ptr(state), state.stride(0), tail_offset, _ptr(proj), proj.stride(0), _ptr(cu_seqlens),
+                     _ptr(positions), _ptr(token_slot), n_seqs, channels, taps, _stream())
+
+
+def delta_scan(out, qn, kn, vc, beta, decay, state, cu_seqlens, positions, token_slot, n_seqs, heads,
+               kv_heads, dim, vdim, n_tokens=0):
+    """The recurrence over every sequence's tokens; S [heads, vdim, rows] at the start of a slot's state
+    is read and written back."""
+    _need_cuda(out, qn, kn, vc, beta, decay, state, cu_seqlens, positions, token_slot)
+    if lib.recording():
+        lib.annotate(bytes=4 * (n_tokens * (2 * kv_heads * dim + heads * dim + 2 * heads * vdim + heads)
+                                + 2 * n_seqs * heads * vdim * delta_state_rows(dim)),
+                     flops=6 * n_tokens * heads * dim * vdim)
+    _delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay), _ptr(state), state.stride(0),
+                _ptr(cu_seqlens), _ptr(positions), _ptr(token_slot), n_seqs, heads, kv_heads, dim, vdim,
+                _stream())
+
+
+def delta_out_norm(y, o, proj, g2t, w, eps, positions, n_tokens, shape):
+    """y = o / rms(o) per head * w * sigmoid(g2 . g1) in the activation type."""
+    _need_cuda(y, o, proj, g2t, w, positions)
+    _need(o.dtype == proj.dtype == g2t.dtype == w.dtype == torch.float32 and y.is_contiguous() and o.is_contiguous(),
+          "delta_out_norm: 32-bit inputs")
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * o.shape[-1] * (4 + y.element_size()) + 4 * g2t.numel())
+    _delta_out_norm[y.dtype](_ptr(y), _ptr(o), _ptr(proj), proj.stride(0), _ptr(g2t), _ptr(w), float(eps),
+                             _ptr(positions), n_tokens, *[int(v) for v in shape], _stream())
+
+
+# ------------------------------------------------------------------ routed experts
+_moe_route = Function("moe", "ek_moe_route", [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P])
+_moe_plan = Function("moe", "ek_moe_plan", [_P, _P, _P, _P, c_int, c_int, _P])
+_moe_up = _per_dtype("moe", "ek_moe_expert_up", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+_moe_down = _per_dtype("moe", "ek_moe_expert_down", [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
+_moe_combine = _per_dtype("moe", "ek_moe_combine", [_P, _P, c_int, c_int, c_int, _P])
+MOE_TILE_ROWS = 32          # must equal kTileRows in csrc/moe.cu
+EXPERT_ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    """Most row tiles a plan of ``n_pairs`` (token, choice) pairs can have."""
+    return -(-n_pairs // MOE_TILE_ROWS) + min(n_experts, n_pairs)
+
+
+def moe_route(sel_expert, sel_weight, logits, n_tokens, n_groups, keep, top, scale):
+    """Router: ``logits`` [T, E] 32-bit -> the ``top`` chosen experts and their weights per token."""
+    _need_cuda(sel_expert, sel_weight, logits)
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and sel_expert.dtype == torch.int32
+          and sel_weight.dtype == torch.float32, "moe_route: 32-bit logits and weights, int32 choices")
+    _moe_route(_ptr(sel_expert), _ptr(sel_weight), _ptr(logits), n_tokens, logits.shape[-1], n_groups, keep,
+               top, float(scale), _stream())
+
+
+def moe_plan(sorted_pair, tiles, n_tiles, sel_expert, n_pairs, n_experts):
+    _need_cuda(sorted_pair, tiles, n_tiles, sel_expert)
+    _moe_plan(_ptr(sorted_pair), _ptr(tiles), _ptr(n_tiles), _ptr(sel_expert), n_pairs, n_experts, _stream())
+
+
+def moe_expert_up(out, x, w, tiles, n_tiles, sorted_pair, n_pairs, top, activation):
+    """out[sorted row] = act(x[token of the pair] . w[expert]^T); ``w`` [E, N, K]."""
+    _need_cuda(out, x, w, tiles, n_tiles, sorted_pair)
+    _need(out.dtype == x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous() and out.is_contiguous(),
+          "moe_expert_up: one dtype, contiguous")
+    e, n, k = w.shape
+    if lib.recording():
+        lib.annotate(bytes=x.element_size() * (min(e, n_pairs) * n * k + n_pairs * (n + k)), flops=2 * n_pairs * n * k)
+    _moe_up[x.dtype](_ptr(out), _ptr(x), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
+                     moe_max_tiles(n_pairs, e), top, n, k, EXPERT_ACTIVATIONS[activation], _stream())
+
+
+def moe_expert_down(pair_out, a, w, tiles, n_tiles, sorted_pair, pair_weight, n_pairs):
+    """pair_out[pair] = weight[pair] * (a[sorted row] . w[expert]^T) in 32-bit; ``w`` [E, N, K]."""
+    _need_cuda(pair_out, a, w, tiles, n_tiles, sorted_pair, pair_weight)
+    _need(a.dtype == w.dtype and pair_out.dtype == torch.float32 and a.is_contiguous() and w.is_contiguous(),
+          "moe_expert_down: 32-bit output")
+    e, n, k = w.shape
+    if lib.recording():
+        lib.annotate(bytes=a.element_size() * (min(e, n_pairs) * n * k + n_pairs * k) + 4 * n_pairs * n,
+                     flops=2 * n_pairs * n * k)
+    _moe_down[a.dtype](_ptr(pair_out), _ptr(a), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
+                       _ptr(pair_weight), moe_max_tiles(n_pairs, e), n, k, _stream())
+
+
+def moe_combine(out, pair_out, n_tokens, top):
+    _need_cuda(out, pair_out)
+    width = out.shape[-1]
+    if lib.recording():
+        lib.annotate(bytes=n_tokens * width * (4 * top + out.element_size()))
+    _moe_combine[out.dtype](_ptr(out), _ptr(pair_out), n_tokens, top, width, _stream())
 
 
 def build_all():

@@ -222,5 +222,17 @@ class Block(Part):
         :class:`DeferredNorm` made for it (then ``forward`` also takes ``next_norm=``); else None."""
         return None
 
+    def open_stream(self, stream, ctx: StepContext):
+        """Called on the first scheduled block with the embedding output [T, hidden] (32-bit): what
+        the blocks carry from layer to layer.  The default is that tensor itself; an arrangement
+        with several residual streams returns its own (every block of a model must then be of
+        that arrangement)."""
+        return stream
+
+    def collapse(self, stream, pending, ctx: StepContext):
+        """Called on the last scheduled block with what the blocks carried and the last ``pending``:
+        returns (stream [T, hidden] in 32-bit, pending) for the final norm."""
+        return stream, pending
+
     def forward(self, stream, pending, ctx: StepContext, entry, writes_cache: bool):
         raise NotImplementedError

@@ -45,3 +45,63 @@ class RopeNeox(PositionEncoding):
                             freqs.sin().to(self.device).contiguous())
         self.cos, self.sin = _TABLES[key]
         self.num_positions = max_positions
+
+
+@register_part("position", "rope_stretched")
+class RopeStretched(PositionEncoding):
+    """NeoX-paired rotation whose slow dimensions turn ``factor`` times slower (YaRN).
+
+    With f_i = theta^(-2i/rot) for i < rot/2: let dim(t) = rot ln(original / (2 pi t)) / (2 ln theta),
+    lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), rot - 1) and ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1).  Dimension i turns by position * (f_i / factor * ramp_i + f_i (1 - ramp_i)),
+    and cosines and sines are multiplied by 0.1 ln(factor) + 1.  Parameters: ``rotary_dim`` (rot),
+    ``theta``, and ``factor``, ``original``, ``fast``, ``slow`` (without ``factor``: the plain rotation).
+    The tables are worked out in 64-bit on the host and kept in 32-bit, with the factor on cos and sin
+    folded in, so the kernels that read ``cos`` / ``sin`` need to know nothing of it.
+    """
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.rotary_dim = int(self.param("rotary_dim"))
+        self.theta = float(self.param("theta"))
+        self.factor = spec.params.get("factor")
+        if self.rotary_dim % 2 or self.rotary_dim < 0:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even")
+        if self.factor is not None:
+            self.factor = float(self.factor)
+            self.original = float(self.param("original"))
+            self.fast, self.slow = float(self.param("fast")), float(self.param("slow"))
+            if not (self.factor > 0 and self.original > 0 and self.fast > 0 and self.slow > 0):
+                raise ValueError("rope_stretched: factor, original, fast and slow must be positive")
+        self.cos = self.sin = None
+        self.num_positions = 0
+
+    def frequencies(self):
+        """(frequencies [rot/2] in 64-bit, factor on cos and sin)."""
+        import math
+        rot, half = self.rotary_dim, self.rotary_dim // 2
+        i = torch.arange(half, dtype=torch.float64)
+        f = self.theta ** (-2.0 * i / max(rot, 1))
+        if self.factor is None:
+            return f, 1.0
+
+        def dim_of(turns):
+            return rot * math.log(self.original / (2 * math.pi * turns)) / (2 * math.log(self.theta))
+
+        lo = max(math.floor(dim_of(self.fast)), 0)
+        hi = min(math.ceil(dim_of(self.slow)), rot - 1)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp), 0.1 * math.log(self.factor) + 1.0
+
+    def prepare(self, max_positions: int) -> None:
+        key = ("stretched", str(self.device), self.theta, self.rotary_dim, max_positions, self.factor,
+               getattr(self, "original", None), getattr(self, "fast", None), getattr(self, "slow", None))
+        if key not in _TABLES:
+            f, mult = self.frequencies()
+            ang = torch.outer(torch.arange(max_positions, dtype=torch.float64), f)
+            if len(_TABLES) > 8:
+                _TABLES.clear()
+            _TABLES[key] = ((ang.cos() * mult).to(torch.float32).to(self.device).contiguous(),
+                            (ang.sin() * mult).to(torch.float32).to(self.device).contiguous())
+        self.cos, self.sin = _TABLES[key]
+        self.num_positions = max_positions

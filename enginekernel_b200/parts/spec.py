@@ -15,7 +15,9 @@ from typing import Dict, List, Optional, Tuple
 
 @dataclasses.dataclass(frozen=True)
 class TensorSpec:
-    """One checkpoint tensor a part reads, by its full name in the safetensors files."""
+    """One checkpoint tensor a part reads, by its full name in the safetensors files.  A size of
+    -1 in ``shape`` is free: the file decides it (the part reads it off the tensor it is handed);
+    random weights take ``free_size`` there."""
     name: str
     shape: Tuple[int, ...]
     #: how the random-weights mode fills it: "linear" and "embedding" are N(0, std),
@@ -25,6 +27,15 @@ class TensorSpec:
     numeric: str = "float"
     #: another tensor name that may stand in when this one is absent (tied weights)
     optional_alias: Optional[str] = None
+    #: what a free size (-1 in ``shape``) becomes when weights are drawn at random
+    free_size: int = 16
+
+    def concrete_shape(self) -> Tuple[int, ...]:
+        return tuple(self.free_size if d < 0 else d for d in self.shape)
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w < 0 or w == g for w, g in zip(self.shape, shape))
 
 
 @dataclasses.dataclass(frozen=True)
@@ -122,7 +133,9 @@ class CacheSpec:
     """What one cache entry of a mixer needs per sequence.
 
     ``kind="kv"``: keys and values of ``heads`` x ``head_dim`` per token, all of them
-    or only the last ``window`` tokens.  ``kind="state"``: one tensor of fixed
+    or only the last ``window`` tokens; ``planes=1``: one row per token and head instead of a key
+    and a value row (a mixer whose keys and values are read from the same cached vector).
+    ``kind="state"``: one tensor of fixed
     ``shape`` per sequence (32-bit unless ``state_dtype`` says otherwise), zeroed when
     a sequence takes the slot.  Entries with equal specs form one group with storage
     of its own.
@@ -133,6 +146,7 @@ class CacheSpec:
     window: Optional[int] = None
     shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
+    planes: int = 2
 
     def group_key(self):
-        return (self.kind, self.heads, self.head_dim, self.window, self.shape, self.state_dtype)
+        return (self.kind, self.heads, self.head_dim, self.window, self.shape, self.state_dtype, self.planes)

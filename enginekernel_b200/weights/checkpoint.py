@@ -90,9 +90,9 @@ def check_against(index: CheckpointIndex, expected: Mapping[str, TensorSpec],
     for name, spec in expected.items():
         if name not in index.file_of:
             continue
-        if tuple(index.shape_of[name]) != tuple(spec.shape):
+        if not spec.fits(index.shape_of[name]):
             wrong_shape.append(f"{name}: file has {list(index.shape_of[name])}, "
-                               f"model needs {list(spec.shape)}")
+                               f"model needs {['any' if d < 0 else d for d in spec.shape]}")
         tag = index.dtype_of[name]
         want = _FLOAT_TAGS if spec.numeric == "float" else _INT_TAGS
         if tag not in want:

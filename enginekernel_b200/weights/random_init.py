@@ -31,10 +31,10 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, dtype=torch.bf
     for name in sorted(expected):
         spec = expected[name]
         if spec.numeric == "int":
-            out[name] = torch.randint(0, vocab_for_int_tables, spec.shape, generator=gen,
+            out[name] = torch.randint(0, vocab_for_int_tables, spec.concrete_shape(), generator=gen,
                                       device=dev, dtype=torch.int32)
             continue
-        t = torch.randn(spec.shape, generator=gen, device=dev, dtype=torch.float32)
+        t = torch.randn(spec.concrete_shape(), generator=gen, device=dev, dtype=torch.float32)
         if spec.init == "gain":
             t.mul_(GAIN_STD).add_(1.0)
         else:
