@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--shape 4b|8b|0.6b] [--impl ours|reference]
                     [--batch B] [--layers L] [--skip-points] [--skip-kernels]
     python bench.py --design lopazen [--sizes 0.6b,4b,1b-h64] [--layers L] [--batch B] [--skip-kernels]
+    python bench.py --design susalorn [--sizes 1b,2b-dense] [--layers L] [--batch B] [--skip-kernels]
 
 The shapes and workloads are the ones BASELINE.json names (its configs[2], [3], [4]):
 
@@ -23,6 +24,9 @@ step and of the prompt step on its own (:mod:`enginekernel_b200.measure`) agains
 peaks.  ``--design lopazen`` leaves that workload alone and instead measures the Lopazen decoder
 beside the Qwen3 decoder at equal layer sizes (12 layers unless ``--layers`` says otherwise): a
 2,048-token prompt step, decode steps of a batch of 8, and both per-kernel tables for each.
+``--design susalorn`` does the same for the Susalorn decoder (alternating latent-attention and
+delta-rule layers over four residual streams, routed or dense feed-forwards) beside a Qwen3 decoder
+of the same width, layer count and feed-forward work per token.
 One line of JSON is printed.  The inputs of a step (gigabytes of weights) are larger than
 the L2.
 
@@ -333,6 +337,55 @@ def design_configs(size: dict, layers: int, context: int):
     return lopazen, qwen3
 
 
+# Susalorn at sizes that resemble real layers, each beside a Qwen3 decoder of the same width whose dense
+# feed-forward does the work of the experts a token is sent to (ff = top * expert ff * 2 / 3: a gated
+# feed-forward has three matrices where an expert has two).  The cached row of the latent attention
+# (kv_rank + rot_dim) is 256 values, the most the attention kernels take.
+SUSALORN_SIZES = {
+    "1b": dict(width=2048, vocab=128256,
+               latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=192),
+               delta=dict(heads=16, kv_heads=16, dim=128, vdim=128, conv=4, rank=64),
+               moe=dict(experts=32, ff=1024, top=4, groups=(4, 2)),
+               qwen3=dict(heads=16, kv_heads=8, dim=128, ff=2816)),
+    "2b-dense": dict(width=2560, vocab=151936,
+                     latent=dict(heads=20, dim=128, rot_dim=64, vdim=128, q_rank=1024, kv_rank=192),
+                     delta=dict(heads=20, kv_heads=10, dim=128, vdim=128, conv=4, rank=80),
+                     dense=6912, qwen3=dict(heads=20, kv_heads=10, dim=128, ff=6912)),
+}
+
+
+def susalorn_configs(size: dict, layers: int, context: int):
+    """(Susalorn configuration, Qwen3 configuration) of one size: latent-attention and delta-rule layers
+    in turn, every one with the size's feed-forward, four residual streams."""
+    from enginekernel_b200.config import Qwen3Config, SusalornConfig
+    la, de = size["latent"], size["delta"]
+    if "moe" in size:
+        m = size["moe"]
+        mlp = {"kind": "moe", "expert": {"ff": m["ff"]},
+               "router": {"experts": m["experts"], "top": m["top"], "scale": 2.5,
+                          "groups": {"count": m["groups"][0], "keep": m["groups"][1]}}}
+    else:
+        mlp = {"kind": "dense", "ff": size["dense"]}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": dict(la, scale=(la["dim"] + la["rot_dim"]) ** -0.5,
+                            rot={"base": 10000.0, "dims": la["rot_dim"],
+                                 "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}})}
+    delta = {"type": "channel_delta", "mlp": mlp, "mixer": dict(de)}
+    susalorn = SusalornConfig.from_dict({
+        "architecture": "Susalorn", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6},
+        "streams": 4, "layers": [delta if i % 2 == 0 else latent for i in range(layers)]})
+    q = size["qwen3"]
+    qwen3 = Qwen3Config.from_dict({
+        "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": layers, "hidden_size": size["width"],
+        "num_attention_heads": q["heads"], "num_key_value_heads": q["kv_heads"], "head_dim": q["dim"],
+        "intermediate_size": q["ff"], "vocab_size": size["vocab"], "rope_theta": 1000000.0,
+        "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": context})
+    return susalorn, qwen3
+
+
+DESIGNS = {"lopazen": (DESIGN_SIZES, design_configs), "susalorn": (SUSALORN_SIZES, susalorn_configs)}
+
+
 def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, with_kernels):
     """Prompt step and decode step of one model: milliseconds, tokens a second, per-kernel tables."""
     import torch
@@ -379,8 +432,16 @@ def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, wi
         out["decode_tok_s"] = batch / (out["decode_ms"] / 1e3)
         out["decode_steps"], out["launches_per_step"] = k, st.launches_per_step
         weight_bytes = engine.model.weight_bytes_read_per_step()
-        kv = sum(2 * 2 * batch * (prompt_len + warmup + stretches * k // 2) * cs.heads * cs.head_dim
-                 for cs in engine.model.cache_entry_specs() if cs is not None)
+        live = prompt_len + warmup + stretches * k // 2
+        kv = 0                                       # what a step reads of the cache: pages, or a state both ways
+        for cs in engine.model.cache_entry_specs():
+            if cs is not None and cs.kind == "kv":
+                kv += cs.planes * 2 * batch * live * cs.heads * cs.head_dim
+            elif cs is not None:
+                size = 1
+                for d in cs.shape:
+                    size *= d
+                kv += 2 * 4 * batch * size
         out["decode_frac_of_copy_bandwidth"] = (weight_bytes + kv) / (out["decode_ms"] / 1e3) / 1e9 / pk["hbm_gbs"]
         if with_kernels:
             out["decode_kernels"] = measure.decode_step_table(st, pk)
@@ -399,7 +460,7 @@ def measure_design(cfg, vocab, batch, prompt_len, context, steps, warmup, pk, wi
 
 
 def run_designs(args) -> int:
-    """``--design lopazen``: the Lopazen decoder beside the Qwen3 decoder at equal layer sizes."""
+    """``--design NAME``: that decoder beside the Qwen3 decoder at equal layer sizes."""
     import torch
     if not torch.cuda.is_available():
         print(json.dumps({"design": args.design, "unavailable": "no CUDA device here"}))
@@ -412,16 +473,17 @@ def run_designs(args) -> int:
     sampler = ClockSampler()
     sampler.start()
     sizes = {}
-    for name in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
-        size = DESIGN_SIZES[name]
-        lopazen, qwen3 = design_configs(size, layers, context)
+    design_sizes, make_configs = DESIGNS[args.design]
+    for name in (args.sizes.split(",") if args.sizes else list(design_sizes)):
+        size = design_sizes[name]
+        design, qwen3 = make_configs(size, layers, context)
         sizes[name] = {"size": size, "layers": layers}
-        for tag, cfg in (("lopazen", lopazen), ("qwen3", qwen3)):
+        for tag, cfg in ((args.design, design), ("qwen3", qwen3)):
             sizes[name][tag] = measure_design(cfg, size["vocab"], batch, prompt_len, context, steps,
                                               max(3, args.warmup), pk, not args.skip_kernels)
-        a, b = sizes[name]["lopazen"], sizes[name]["qwen3"]
-        sizes[name]["lopazen_over_qwen3"] = {"prefill_tok_s": a["prefill_tok_s"] / b["prefill_tok_s"],
-                                             "decode_tok_s": a["decode_tok_s"] / b["decode_tok_s"]}
+        a, b = sizes[name][args.design], sizes[name]["qwen3"]
+        sizes[name][args.design + "_over_qwen3"] = {"prefill_tok_s": a["prefill_tok_s"] / b["prefill_tok_s"],
+                                                    "decode_tok_s": a["decode_tok_s"] / b["decode_tok_s"]}
     print(json.dumps({
         "design": args.design, "beside": "qwen3", "dtype": "bf16", "n_gpus": 1,
         "data": "synthetic: seeded random weights and uniform random token ids",
@@ -447,7 +509,7 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-kernels", action="store_true", help="leave out the per-kernel tables")
     ap.add_argument("--prefill-seqs", type=int, default=1,
                     help="sequences of 2,048 tokens in the prompt step of the per-kernel table")
-    ap.add_argument("--design", default="", choices=["", "lopazen"],
+    ap.add_argument("--design", default="", choices=["", "lopazen", "susalorn"],
                     help="instead of the default workload: this design beside the Qwen3 decoder at "
                          "equal layer sizes (prompt step, decode step, per-kernel tables)")
     ap.add_argument("--sizes", default="", help="with --design: comma-separated names of DESIGN_SIZES")

@@ -330,7 +330,8 @@ EK_EXPORT int ek_delta_scan(float* out, const float* qn, const float* kn, const 
   using namespace ek;
   if (n_seqs <= 0) return 0;
   DeltaShape sh{heads, kv_heads, dim, vdim, 1, 1, 1};
-  if (!shape_ok(sh) || n_seqs > 2147483647 / 1) return EK_ERR_ARG;
+  // S is read and written four values at a time: every slot's S must start on a 16-byte boundary
+  if (!shape_ok(sh) || slot_stride % 4 || ((uintptr_t)state & 15)) return EK_ERR_ARG;
   dim3 grid(n_seqs, heads, (vdim + kScanCols - 1) / kScanCols);
   if (grid.z > 65535) return EK_ERR_ARG;
   const int rows = ek_delta_state_rows(dim);

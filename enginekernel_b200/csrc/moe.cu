@@ -7,10 +7,12 @@
 //             scores / (their sum + 1e-20) * scale.  A warp a token.
 //   plan      the (token, choice) pairs sorted by expert, and the row tiles of every expert's
 //             stretch, made on the device: the host never sees who chose what.
-//   expert product  out[row] = f(x[row] . W_e^T) over the tiles of the plan, FFMA with 32-bit
-//             sums in ascending k, so a pair's result does not depend on its neighbours; the up
-//             form gathers its rows by token and applies the activation, the down form scales by
-//             the pair's weight and scatters 32-bit rows by pair.
+//   expert product  out[row] = f(x[row] . W_e^T) over the tiles of the plan: FFMA with 32-bit
+//             sums in ascending k (the 32-bit path, and 16-bit rows that cannot be read 16 bytes
+//             at a time), or mma.sync on bfloat16 tiles with 32-bit accumulators; either way a
+//             pair's result does not depend on its neighbours.  The up form gathers its rows by
+//             token and applies the activation, the down form scales by the pair's weight and
+//             scatters 32-bit rows by pair.
 //   combine   out[t] = sum over the token's choices, in the order they were chosen.
 #include "common.cuh"
 
@@ -90,7 +92,7 @@ moe_route_kernel(int* __restrict__ sel_expert, float* __restrict__ sel_weight,
   for (int k = lane; k < top; k += 32) sel_weight[(size_t)t * top + k] *= f;
 }
 
-constexpr int kTileRows = 32;
+constexpr int kTileRows = 64;
 
 // One block.  sel_expert [P] -> sorted_pair [P] (pairs grouped by expert), tiles [max_tiles][3] =
 // (expert, first sorted row, rows), n_tiles[0].
@@ -155,7 +157,7 @@ moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, cons
                           const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                           const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
                           int top, int N, int K, int act) {
-  constexpr int BM = kTileRows, BN = 64, BK = 16, TM = 2, TN = 4, PAD = 4;
+  constexpr int BM = kTileRows, BN = 64, BK = 16, TM = 4, TN = 4, PAD = 4;
   __shared__ __align__(16) float As[BK][BM + PAD];
   __shared__ __align__(16) float Ws[BK][BN + PAD];
   __shared__ int src_row[BM];
@@ -223,6 +225,111 @@ moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, cons
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product on the tensor cores (bfloat16 operands, 32-bit accumulators): a block takes a
+// 64-row tile of the plan and 128 columns, eight warps of 32 x 32 each, K in steps of 32 through
+// shared memory (rows padded by 16 bytes: ldmatrix without bank conflicts).  K % 8 == 0.
+__device__ __forceinline__ void ldsm_x4(uint32_t r[4], const bf16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool UP>
+__global__ void __launch_bounds__(256)
+moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a, const bf16* __restrict__ w,
+                             const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                             const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
+                             int top, int N, int K, int act) {
+  constexpr int BM = kTileRows, BN = 128, BK = 32, LD = BK + 8;
+  __shared__ __align__(16) bf16 As[BM][LD];
+  __shared__ __align__(16) bf16 Ws[BN][LD];
+  __shared__ int src_row[BM];
+  __shared__ int pair_s[BM];
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.x >= n_tiles[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < BM) {
+    const int p = tid < rows ? sorted_pair[row0 + tid] : -1;
+    pair_s[tid] = p;
+    src_row[tid] = p < 0 ? -1 : (UP ? p / top : row0 + tid);
+  }
+  __syncthreads();
+  const int n0 = blockIdx.y * BN;
+  const bf16* we = w + (size_t)e * N * K;
+  const int wm = warp >> 2, wn = warp & 3;      // the warp's 32 x 32 piece: rows wm * 32, columns wn * 32
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    {                                            // A: 64 rows x 4 chunks of 8 values
+      const int row = tid >> 2, ch = tid & 3;
+      const int src = src_row[row], gk = k0 + ch * 8;
+      const uint4 v = (src >= 0 && gk < K) ? *reinterpret_cast<const uint4*>(a + (size_t)src * K + gk) : zero;
+      *reinterpret_cast<uint4*>(&As[row][ch * 8]) = v;
+    }
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {             // W: 128 rows x 4 chunks
+      const int idx = tid + it * 256;
+      const int row = idx >> 2, ch = idx & 3;
+      const int gn = n0 + row, gk = k0 + ch * 8;
+      const uint4 v = (gn < N && gk < K) ? *reinterpret_cast<const uint4*>(we + (size_t)gn * K + gk) : zero;
+      *reinterpret_cast<uint4*>(&Ws[row][ch * 8]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t af[2][4], bfr[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)                // rows (lane % 16), k half (lane / 16)
+        ldsm_x4(af[i], &As[wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)                // two n8 tiles a load: n = (lane / 16) * 8 + lane % 8, k half (lane / 8) % 2
+        ldsm_x4(bfr[j], &Ws[wn * 32 + j * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          mma_bf16_16816(acc[i][j], af[i], bfr[j >> 1][(j & 1) * 2], bfr[j >> 1][(j & 1) * 2 + 1]);
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + i * 16 + g + half * 8;
+      if (r >= rows) continue;
+      const int p = pair_s[r];
+      const float pw = UP ? 1.f : pair_weight[p];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int gn = n0 + wn * 32 + j * 8 + tq * 2 + c;
+          if (gn >= N) continue;
+          const float v = acc[i][j][half * 2 + c];
+          if (UP) ((bf16*)out_)[(size_t)(row0 + r) * N + gn] = __float2bfloat16_rn(activate(v, act));
+          else ((float*)out_)[(size_t)p * N + gn] = v * pw;
+        }
+    }
+}
+
 // out[t, :] = sum_k pair_out[t * top + k, :], k ascending.
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ pair_out, int top,
@@ -265,6 +372,33 @@ EK_EXPORT int ek_moe_plan(int* sorted_pair, int* tiles, int* n_tiles, const int*
   if (E <= 0 || E > 8192) return EK_ERR_ARG;
   ek::moe_plan_kernel<<<1, 1024, (size_t)(3 * E + 1) * sizeof(int), stream>>>(sorted_pair, tiles, n_tiles,
                                                                              sel_expert, P, E);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+// The tensor-core forms: bfloat16, K a multiple of 8, operands on 16-byte boundaries.
+EK_EXPORT int ek_moe_expert_up_tc(void* out, const void* x, const void* w, const int* tiles, const int* n_tiles,
+                                  const int* sorted_pair, int max_tiles, int top, int N, int K, int act,
+                                  cudaStream_t stream) {
+  using namespace ek;
+  if (max_tiles <= 0) return 0;
+  if (N <= 0 || K <= 0 || K % 8 || top <= 0 || (N + 127) / 128 > 65535 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return EK_ERR_ARG;
+  dim3 grid(max_tiles, (N + 127) / 128);
+  moe_expert_product_tc_kernel<true><<<grid, 256, 0, stream>>>(out, (const bf16*)x, (const bf16*)w, tiles, n_tiles,
+                                                              sorted_pair, nullptr, top, N, K, act);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+EK_EXPORT int ek_moe_expert_down_tc(float* out, const void* a, const void* w, const int* tiles, const int* n_tiles,
+                                    const int* sorted_pair, const float* pair_weight, int max_tiles, int N, int K,
+                                    cudaStream_t stream) {
+  using namespace ek;
+  if (max_tiles <= 0) return 0;
+  if (N <= 0 || K <= 0 || K % 8 || (N + 127) / 128 > 65535 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
+    return EK_ERR_ARG;
+  dim3 grid(max_tiles, (N + 127) / 128);
+  moe_expert_product_tc_kernel<false><<<grid, 256, 0, stream>>>(out, (const bf16*)a, (const bf16*)w, tiles, n_tiles,
+                                                               sorted_pair, pair_weight, 1, N, K, 0);
   EK_RETURN_LAUNCH_STATUS();
 }
 

@@ -1132,7 +1132,14 @@ _moe_plan = Function("moe", "ek_moe_plan", [_P, _P, _P, _P, c_int, c_int, _P])
 _moe_up = _per_dtype("moe", "ek_moe_expert_up", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
 _moe_down = _per_dtype("moe", "ek_moe_expert_down", [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
 _moe_combine = _per_dtype("moe", "ek_moe_combine", [_P, _P, c_int, c_int, c_int, _P])
-MOE_TILE_ROWS = 32          # must equal kTileRows in csrc/moe.cu
+_moe_up_tc = Function("moe", "ek_moe_expert_up_tc", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+_moe_down_tc = Function("moe", "ek_moe_expert_down_tc", [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
+
+
+def _moe_on_tensor_cores(a, w) -> bool:
+    """bfloat16 rows that can be read 16 bytes at a time go to the mma.sync form of the expert products."""
+    return (a.dtype == torch.bfloat16 and w.shape[-1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+MOE_TILE_ROWS = 64          # must equal kTileRows in csrc/moe.cu
 EXPERT_ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
 
 
@@ -1163,8 +1170,9 @@ def moe_expert_up(out, x, w, tiles, n_tiles, sorted_pair, n_pairs, top, activati
     e, n, k = w.shape
     if lib.recording():
         lib.annotate(bytes=x.element_size() * (min(e, n_pairs) * n * k + n_pairs * (n + k)), flops=2 * n_pairs * n * k)
-    _moe_up[x.dtype](_ptr(out), _ptr(x), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
-                     moe_max_tiles(n_pairs, e), top, n, k, EXPERT_ACTIVATIONS[activation], _stream())
+    fn = _moe_up_tc if _moe_on_tensor_cores(x, w) else _moe_up[x.dtype]
+    fn(_ptr(out), _ptr(x), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
+       moe_max_tiles(n_pairs, e), top, n, k, EXPERT_ACTIVATIONS[activation], _stream())
 
 
 def moe_expert_down(pair_out, a, w, tiles, n_tiles, sorted_pair, pair_weight, n_pairs):
@@ -1176,8 +1184,9 @@ def moe_expert_down(pair_out, a, w, tiles, n_tiles, sorted_pair, pair_weight, n_
     if lib.recording():
         lib.annotate(bytes=a.element_size() * (min(e, n_pairs) * n * k + n_pairs * k) + 4 * n_pairs * n,
                      flops=2 * n_pairs * n * k)
-    _moe_down[a.dtype](_ptr(pair_out), _ptr(a), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
-                       _ptr(pair_weight), moe_max_tiles(n_pairs, e), n, k, _stream())
+    fn = _moe_down_tc if _moe_on_tensor_cores(a, w) else _moe_down[a.dtype]
+    fn(_ptr(pair_out), _ptr(a), _ptr(w), _ptr(tiles), _ptr(n_tiles), _ptr(sorted_pair),
+       _ptr(pair_weight), moe_max_tiles(n_pairs, e), n, k, _stream())
 
 
 def moe_combine(out, pair_out, n_tokens, top):

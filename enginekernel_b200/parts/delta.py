@@ -68,7 +68,8 @@ class ChannelDelta(Mixer):
         self.dt_bias = self.a_log = self.norm_w = None
 
     def cache_spec(self):
-        return CacheSpec("state", shape=(self.s_values + self.channels * (self.taps - 1),))
+        # (a multiple of four values, so that every slot's S starts on a 16-byte boundary)
+        return CacheSpec("state", shape=(-(-(self.s_values + self.channels * (self.taps - 1)) // 4) * 4,))
 
     def load(self, tensors):
         w, f32 = self.spec.weights, torch.float32

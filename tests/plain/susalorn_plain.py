@@ -236,3 +236,17 @@ def forward(cfg, w, ids, return_layers=False):
     x = xs.sum(1) if n else x
     logits = lin(stream_norm(x, w["final.norm"], eps), w["embed"])
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def logits(cfg, w, ids):
+    return forward(cfg, w, ids)
+
+
+def greedy(cfg, w, ids, n_new):
+    """The n_new tokens that arg-max decoding appends to ids (the whole sequence is run again each time)."""
+    ids, out = list(ids), []
+    for _ in range(n_new):
+        nxt = int(forward(cfg, w, ids)[-1].argmax())
+        out.append(nxt)
+        ids.append(nxt)
+    return out
