@@ -8,11 +8,13 @@
 // group of 8 lanes, the column's d rows spread over the lanes' registers, sequentially over the
 // tokens of a sequence and in parallel over sequences, heads and columns.
 //
-// Four kernels, all taking packed rows of several sequences (prompts, chunks, single tokens):
-//   delta_prepare    convolution + SiLU, unit norms, beta, decays                (a block a token)
+// Five kernels, all taking packed rows of several sequences (prompts, chunks, single tokens):
+//   delta_low_rank   the second halves of the two low-rank pairs: decays and output gates, a tile of
+//                    tokens x channels a block so that a weight is fetched once for 16 tokens
+//   delta_prepare    convolution + SiLU, unit norms, beta                        (a block a token)
 //   delta_conv_tail  the last taps-1 convolution inputs of every sequence -> its state
 //   delta_scan       the recurrence; reads and writes S in the state
-//   delta_out_norm   o / rms(o) * w * sigmoid(gate) per head, to the activation type
+//   delta_out_norm   o / rms(o) * w * gate per head, to the activation type
 // State of a slot (32-bit): [heads][e][DP] for S (DP = d rounded up to the scan's row count), then
 // [channels][taps-1] convolution inputs.  A fresh slot is all zeros.
 // Everything that enters the recurrence is computed and kept in 32-bit.
@@ -36,19 +38,50 @@ struct DeltaShape {
   __host__ __device__ int row() const { return off_g() + rank_g; }
 };
 
+// out[t, c] = f(bias[c] + sum_r w2t[r][c] * proj[t, offset + r]) for c < channels: f = sigmoid (mode 1), or
+// the decay exp(-exp(a_log[c / dim]) * softplus(.)) (mode 0).  grid (token tiles of 16, channel tiles of 128).
+constexpr int kRankTokens = 16;
+__global__ void __launch_bounds__(128)
+delta_low_rank_kernel(float* __restrict__ out, const float* __restrict__ proj, int proj_stride, int offset,
+                      int rank, const float* __restrict__ w2t, const float* __restrict__ bias,
+                      const float* __restrict__ a_log, int dim, int channels, int n_tokens, int mode) {
+  extern __shared__ float x_s[];                // [kRankTokens][rank]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t0 = blockIdx.x * kRankTokens, tid = threadIdx.x;
+  const int nt = min(kRankTokens, n_tokens - t0);
+  for (int idx = tid; idx < kRankTokens * rank; idx += blockDim.x) {
+    const int tt = idx / rank, r = idx % rank;
+    x_s[idx] = tt < nt ? proj[(size_t)(t0 + tt) * proj_stride + offset + r] : 0.f;
+  }
+  __syncthreads();
+  const int c = blockIdx.y * 128 + tid;
+  if (c >= channels) return;
+  float acc[kRankTokens];
+  const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+  for (int tt = 0; tt < kRankTokens; ++tt) acc[tt] = b;
+#pragma unroll 8
+  for (int r = 0; r < rank; ++r) {
+    const float wv = w2t[(size_t)r * channels + c];
+#pragma unroll
+    for (int tt = 0; tt < kRankTokens; ++tt) acc[tt] = fmaf(wv, x_s[tt * rank + r], acc[tt]);
+  }
+  const float rate = mode == 0 ? expf(a_log[c / dim]) : 0.f;
+  for (int tt = 0; tt < nt; ++tt)
+    out[(size_t)(t0 + tt) * channels + c] = mode == 0 ? expf(-rate * softplus_f(acc[tt])) : sigmoid_f(acc[tt]);
+}
+
 // grid: tokens.  proj [T, >= row()] 32-bit.  conv_w [channels][taps] (last column: the current
-// token).  a2t [rank_a][heads * dim], dt_bias [heads * dim], a_log [heads].
-// Outputs (32-bit): qn, kn [T, kv_heads * dim]; vc [T, heads * vdim]; beta [T, heads];
-// decay [T, heads * dim].
+// token).  Outputs (32-bit): qn, kn [T, kv_heads * dim]; vc [T, heads * vdim]; beta [T, heads].
 __global__ void __launch_bounds__(256)
 delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
-                     float* __restrict__ beta, float* __restrict__ decay,
+                     float* __restrict__ beta,
                      const float* __restrict__ proj, int proj_stride, const float* __restrict__ conv_w,
-                     const float* __restrict__ a2t, const float* __restrict__ dt_bias,
-                     const float* __restrict__ a_log, const float* __restrict__ state,
+                     const float* __restrict__ state,
                      size_t slot_stride, size_t tail_offset, const int* __restrict__ positions,
                      const int* __restrict__ token_slot, DeltaShape sh) {
-  extern __shared__ float qk_s[];               // [2 * cq] convolved q and k, then [rank_a]
+  extern __shared__ float qk_s[];               // [2 * cq] convolved q and k
   __shared__ int n_prev_s;
   pdl_launch_dependents();
   pdl_wait();
@@ -62,9 +95,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
     while (n < K - 1 && t - n - 1 >= 0 && token_slot[t - n - 1] == slot && positions[t - n - 1] == pos - n - 1) ++n;
     n_prev_s = n;
   }
-  float* a1_s = qk_s + 2 * cq;
   const float* row = proj + (size_t)t * proj_stride;
-  for (int r = tid; r < sh.rank_a; r += blockDim.x) a1_s[r] = row[sh.off_a() + r];
   __syncthreads();
   const int n_prev = n_prev_s;
   const float* tail = state + (size_t)slot * slot_stride + tail_offset;
@@ -96,15 +127,9 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
   }
   for (int h = tid; h < sh.heads; h += blockDim.x)
     beta[(size_t)t * sh.heads + h] = sigmoid_f(row[sh.off_beta() + h]);
-  const int nd = sh.heads * sh.dim;
-  for (int c = tid; c < nd; c += blockDim.x) {
-    float a = dt_bias[c];
-    for (int r = 0; r < sh.rank_a; ++r) a = fmaf(a2t[(size_t)r * nd + c], a1_s[r], a);
-    decay[(size_t)t * nd + c] = expf(-expf(a_log[c / sh.dim]) * softplus_f(a));
-  }
 }
 
-// grid: sequences.  After the step the state's tail holds the last taps-1 inputs of the sequence.
+// grid (sequences, channel tiles).  After the step the state's tail holds the last taps-1 inputs of the sequence.
 __global__ void delta_conv_tail_kernel(float* __restrict__ state, size_t slot_stride, size_t tail_offset,
                                        const float* __restrict__ proj, int proj_stride,
                                        const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
@@ -116,7 +141,7 @@ __global__ void delta_conv_tail_kernel(float* __restrict__ state, size_t slot_st
   if (n <= 0 || positions[start] < 0) return;
   float* tail = state + (size_t)token_slot[start] * slot_stride + tail_offset;
   const int keep = taps - 1;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     float* tc = tail + (size_t)c * keep;
     for (int m = 0; m < keep; ++m) {
       const int from_step = n - keep + m;       // row of the step that lands at place m
@@ -127,12 +152,17 @@ __global__ void delta_conv_tail_kernel(float* __restrict__ state, size_t slot_st
 
 constexpr int kScanCols = 32;        // columns of S a block takes
 constexpr int kScanLanes = 8;        // lanes that share a column
-constexpr int kScanChunk = 8;        // tokens fetched into shared memory at a time
+constexpr int kScanChunk = 16;       // tokens fetched into shared memory at a time
+constexpr int kScanThreads = kScanCols * kScanLanes;
 
 // grid (sequences, heads, column tiles); 256 threads = 32 columns x 8 lanes; a lane holds RPL
-// consecutive rows of its column.
+// consecutive rows of its column.  The tokens' q, k, decays, v and beta come in chunks of 16 through
+// two shared-memory buffers: while a chunk is worked through, the next one is on its way from global
+// memory into registers and is put down behind the chunk's last token.  Only S^T k lies on the chain
+// from token to token (a lane's share in four independent sums, then three exchanges among the eight
+// lanes); the read-out S^T q is summed beside it.
 template <int RPL>
-__global__ void __launch_bounds__(kScanCols* kScanLanes)
+__global__ void __launch_bounds__(kScanThreads)
 delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const float* __restrict__ kn,
                   const float* __restrict__ vc, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* __restrict__ state, size_t slot_stride,
@@ -141,12 +171,15 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const f
   constexpr int DP = RPL * kScanLanes;          // rows held (>= dim; rows past dim stay zero)
   constexpr int LDS = RPL + 4;                  // a lane's stretch in shared memory, padded
   constexpr int ROW = kScanLanes * LDS;
-  __shared__ __align__(16) float q_s[kScanChunk][ROW];
-  __shared__ __align__(16) float k_s[kScanChunk][ROW];
-  __shared__ __align__(16) float g_s[kScanChunk][ROW];
-  __shared__ float v_s[kScanChunk][kScanCols];
-  __shared__ float o_s[kScanChunk][kScanCols];
-  __shared__ float b_s[kScanChunk];
+  constexpr int PER = kScanChunk * DP / kScanThreads;       // staged values of q (k, g) per thread
+  constexpr int PERV = kScanChunk * kScanCols / kScanThreads;
+  extern __shared__ __align__(16) float scan_s[];
+  float* q_s = scan_s;                          // [2][chunk][ROW]
+  float* k_s = q_s + 2 * kScanChunk * ROW;
+  float* g_s = k_s + 2 * kScanChunk * ROW;
+  float* v_s = g_s + 2 * kScanChunk * ROW;      // [2][chunk][cols]
+  float* b_s = v_s + 2 * kScanChunk * kScanCols;          // [2][chunk]
+  float* o_s = b_s + 2 * kScanChunk;            // [chunk][cols]
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -167,44 +200,67 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const f
     S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
   }
 
-  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+  float rq[PER], rk[PER], rg[PER], rv[PERV], rb = 0.f;
+  auto fetch = [&](int c0) {                    // chunk c0 .. c0+15 of the sequence -> registers
     const int nt = min(kScanChunk, n - c0);
-    for (int idx = tid; idx < kScanChunk * DP; idx += kScanCols * kScanLanes) {
-      const int tt = idx / DP, r = idx % DP;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int idx = tid + i * kScanThreads, tt = idx / DP, r = idx % DP;
       const bool ok = tt < nt && r < sh.dim;
       const size_t rowi = (size_t)(start + c0 + tt);
-      const int at = (r / RPL) * LDS + r % RPL;
-      q_s[tt][at] = ok ? qn[rowi * cq + (size_t)kvh * sh.dim + r] : 0.f;
-      k_s[tt][at] = ok ? kn[rowi * cq + (size_t)kvh * sh.dim + r] : 0.f;
-      g_s[tt][at] = ok ? decay[rowi * nd + (size_t)h * sh.dim + r] : 1.f;
+      rq[i] = ok ? qn[rowi * cq + (size_t)kvh * sh.dim + r] : 0.f;
+      rk[i] = ok ? kn[rowi * cq + (size_t)kvh * sh.dim + r] : 0.f;
+      rg[i] = ok ? decay[rowi * nd + (size_t)h * sh.dim + r] : 1.f;
     }
-    for (int idx = tid; idx < kScanChunk * kScanCols; idx += kScanCols * kScanLanes) {
-      const int tt = idx / kScanCols, c = idx % kScanCols;
+#pragma unroll
+    for (int i = 0; i < PERV; ++i) {
+      const int idx = tid + i * kScanThreads, tt = idx / kScanCols, c = idx % kScanCols;
       const int gc = blockIdx.z * kScanCols + c;
-      v_s[tt][c] = (tt < nt && gc < sh.vdim) ? vc[(size_t)(start + c0 + tt) * cv + (size_t)h * sh.vdim + gc] : 0.f;
+      rv[i] = (tt < nt && gc < sh.vdim) ? vc[(size_t)(start + c0 + tt) * cv + (size_t)h * sh.vdim + gc] : 0.f;
     }
-    if (tid < kScanChunk) b_s[tid] = tid < nt ? beta[(size_t)(start + c0 + tid) * sh.heads + h] : 0.f;
-    __syncthreads();
+    if (tid < kScanChunk) rb = tid < nt ? beta[(size_t)(start + c0 + tid) * sh.heads + h] : 0.f;
+  };
+  auto put = [&](int buf) {                     // registers -> buffer `buf`
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int idx = tid + i * kScanThreads, tt = idx / DP, r = idx % DP;
+      const int at = (buf * kScanChunk + tt) * ROW + (r / RPL) * LDS + r % RPL;
+      q_s[at] = rq[i]; k_s[at] = rk[i]; g_s[at] = rg[i];
+    }
+#pragma unroll
+    for (int i = 0; i < PERV; ++i) v_s[buf * kScanChunk * kScanCols + tid + i * kScanThreads] = rv[i];
+    if (tid < kScanChunk) b_s[buf * kScanChunk + tid] = rb;
+  };
+
+  fetch(0);
+  put(0);
+  __syncthreads();
+  int buf = 0;
+  for (int c0 = 0; c0 < n; c0 += kScanChunk, buf ^= 1) {
+    const int nt = min(kScanChunk, n - c0);
+    const bool more = c0 + kScanChunk < n;
+    if (more) fetch(c0 + kScanChunk);           // in flight while this chunk is worked through
     for (int tt = 0; tt < nt; ++tt) {
-      const float* kk = &k_s[tt][lr * LDS];
-      const float* gg = &g_s[tt][lr * LDS];
-      const float* qq = &q_s[tt][lr * LDS];
-      float part = 0.f;
+      const float* kk = k_s + (buf * kScanChunk + tt) * ROW + lr * LDS;
+      const float* gg = g_s + (buf * kScanChunk + tt) * ROW + lr * LDS;
+      const float* qq = q_s + (buf * kScanChunk + tt) * ROW + lr * LDS;
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
       for (int i = 0; i < RPL; i += 4) {
         const float4 g4 = *reinterpret_cast<const float4*>(gg + i);
         const float4 k4 = *reinterpret_cast<const float4*>(kk + i);
         S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
-        part = fmaf(S[i], k4.x, part);
-        part = fmaf(S[i + 1], k4.y, part);
-        part = fmaf(S[i + 2], k4.z, part);
-        part = fmaf(S[i + 3], k4.w, part);
+        p0 = fmaf(S[i], k4.x, p0);
+        p1 = fmaf(S[i + 1], k4.y, p1);
+        p2 = fmaf(S[i + 2], k4.z, p2);
+        p3 = fmaf(S[i + 3], k4.w, p3);
       }
+      float part = (p0 + p1) + (p2 + p3);
       part += __shfl_xor_sync(0xffffffffu, part, 1);
       part += __shfl_xor_sync(0xffffffffu, part, 2);
       part += __shfl_xor_sync(0xffffffffu, part, 4);
-      const float u = b_s[tt] * (v_s[tt][cl] - part);
-      float po = 0.f;
+      const float u = b_s[buf * kScanChunk + tt] * (v_s[(buf * kScanChunk + tt) * kScanCols + cl] - part);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int i = 0; i < RPL; i += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kk + i);
@@ -213,24 +269,25 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const f
         S[i + 1] = fmaf(k4.y, u, S[i + 1]);
         S[i + 2] = fmaf(k4.z, u, S[i + 2]);
         S[i + 3] = fmaf(k4.w, u, S[i + 3]);
-        po = fmaf(S[i], q4.x, po);
-        po = fmaf(S[i + 1], q4.y, po);
-        po = fmaf(S[i + 2], q4.z, po);
-        po = fmaf(S[i + 3], q4.w, po);
+        o0 = fmaf(S[i], q4.x, o0);
+        o1 = fmaf(S[i + 1], q4.y, o1);
+        o2 = fmaf(S[i + 2], q4.z, o2);
+        o3 = fmaf(S[i + 3], q4.w, o3);
       }
+      float po = (o0 + o1) + (o2 + o3);
       po += __shfl_xor_sync(0xffffffffu, po, 1);
       po += __shfl_xor_sync(0xffffffffu, po, 2);
       po += __shfl_xor_sync(0xffffffffu, po, 4);
-      if (lr == 0) o_s[tt][cl] = po;
+      if (lr == 0) o_s[tt * kScanCols + cl] = po;
     }
+    if (more) put(buf ^ 1);                     // (the other buffer: nobody reads it during this chunk)
     __syncthreads();
-    for (int idx = tid; idx < nt * kScanCols; idx += kScanCols * kScanLanes) {
+    for (int idx = tid; idx < nt * kScanCols; idx += kScanThreads) {
       const int tt = idx / kScanCols, c = idx % kScanCols;
       const int gc = blockIdx.z * kScanCols + c;
-      if (gc < sh.vdim) out[(size_t)(start + c0 + tt) * cv + (size_t)h * sh.vdim + gc] = o_s[tt][c];
+      if (gc < sh.vdim) out[(size_t)(start + c0 + tt) * cv + (size_t)h * sh.vdim + gc] = o_s[idx];
     }
-    // (the next chunk's loads touch q_s, k_s, g_s, v_s, b_s only, and o_s is next written after
-    // the barrier that follows those loads)
+    __syncthreads();                            // o_s is written again in the next chunk
   }
   if (live) {
 #pragma unroll
@@ -239,13 +296,29 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const f
   }
 }
 
-// grid: tokens.  y[t, h, j] = o[t, h, j] / rms_j(o[t, h, :]) * w[j] * sigmoid(sum_r g2t[r][h, j] g1[t, r]).
+template <int RPL>
+static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, float* out, const float* qn, const float* kn,
+                               const float* vc, const float* beta, const float* decay, float* state,
+                               size_t slot_stride, const int* cu_seqlens, const int* positions,
+                               const int* token_slot, DeltaShape sh) {
+  constexpr int ROW = kScanLanes * (RPL + 4);
+  const size_t smem = sizeof(float) * (size_t)(6 * kScanChunk * ROW + 2 * kScanChunk * kScanCols + 2 * kScanChunk +
+                                               kScanChunk * kScanCols);
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  delta_scan_kernel<RPL><<<grid, kScanThreads, smem, stream>>>(out, qn, kn, vc, beta, decay, state, slot_stride,
+                                                              cu_seqlens, positions, token_slot, sh);
+  return cudaGetLastError();
+}
+
+// grid: tokens.  y[t, h, j] = o[t, h, j] / rms_j(o[t, h, :]) * w[j] * gate[t, h, j].
 template <typename T>
 __global__ void __launch_bounds__(256)
-delta_out_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ proj,
-                      int proj_stride, const float* __restrict__ g2t, const float* __restrict__ w,
-                      float eps, const int* __restrict__ positions, DeltaShape sh) {
-  extern __shared__ float g1_s[];               // [rank_g]
+delta_out_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const float* __restrict__ gate,
+                      const float* __restrict__ w, float eps, const int* __restrict__ positions,
+                      DeltaShape sh) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, tid = threadIdx.x;
@@ -254,8 +327,6 @@ delta_out_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const floa
     for (int c = tid; c < cv; c += blockDim.x) y[(size_t)t * cv + c] = from_f<T>(0.f);
     return;
   }
-  for (int r = tid; r < sh.rank_g; r += blockDim.x) g1_s[r] = proj[(size_t)t * proj_stride + sh.off_g() + r];
-  __syncthreads();
   const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   for (int h = warp; h < sh.heads; h += nwarps) {
     const float* x = o + (size_t)t * cv + (size_t)h * sh.vdim;
@@ -265,9 +336,7 @@ delta_out_norm_kernel(T* __restrict__ y, const float* __restrict__ o, const floa
     const float inv = rsqrtf(ss / (float)sh.vdim + eps);
     for (int j = lane; j < sh.vdim; j += 32) {
       const int c = h * sh.vdim + j;
-      float gate = 0.f;
-      for (int r = 0; r < sh.rank_g; ++r) gate = fmaf(g2t[(size_t)r * cv + c], g1_s[r], gate);
-      y[(size_t)t * cv + c] = from_f<T>(x[j] * inv * w[j] * sigmoid_f(gate));
+      y[(size_t)t * cv + c] = from_f<T>(x[j] * inv * w[j] * gate[(size_t)t * cv + c]);
     }
   }
 }
@@ -288,9 +357,28 @@ EK_EXPORT int ek_delta_state_rows(int dim) {
   return 256;
 }
 
-EK_EXPORT int ek_delta_prepare(float* qn, float* kn, float* vc, float* beta, float* decay,
-                               const float* proj, int proj_stride, const float* conv_w, const float* a2t,
-                               const float* dt_bias, const float* a_log, const float* state,
+// mode 0: decays (bias = dt_bias, a_log per head of `dim` channels); mode 1: sigmoid gates.
+EK_EXPORT int ek_delta_low_rank(float* out, const float* proj, int proj_stride, int offset, int rank,
+                                const float* w2t, const float* bias, const float* a_log, int dim,
+                                int channels, int n_tokens, int mode, cudaStream_t stream) {
+  using namespace ek;
+  if (n_tokens <= 0) return 0;
+  if (rank <= 0 || rank > 2048 || channels <= 0 || dim <= 0 || offset < 0 || proj_stride < offset + rank ||
+      (mode == 0 && !a_log) || (channels + 127) / 128 > 65535)
+    return EK_ERR_ARG;
+  dim3 grid((n_tokens + kRankTokens - 1) / kRankTokens, (channels + 127) / 128);
+  const size_t smem = (size_t)kRankTokens * rank * sizeof(float);
+  if (smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_low_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  delta_low_rank_kernel<<<grid, 128, smem, stream>>>(out, proj, proj_stride, offset, rank, w2t, bias, a_log, dim,
+                                                     channels, n_tokens, mode);
+  EK_RETURN_LAUNCH_STATUS();
+}
+
+EK_EXPORT int ek_delta_prepare(float* qn, float* kn, float* vc, float* beta,
+                               const float* proj, int proj_stride, const float* conv_w, const float* state,
                                long long slot_stride, long long tail_offset, const int* positions,
                                const int* token_slot, int n_tokens, int heads, int kv_heads, int dim,
                                int vdim, int taps, int rank_a, int rank_g, cudaStream_t stream) {
@@ -298,15 +386,15 @@ EK_EXPORT int ek_delta_prepare(float* qn, float* kn, float* vc, float* beta, flo
   if (n_tokens <= 0) return 0;
   DeltaShape sh{heads, kv_heads, dim, vdim, taps, rank_a, rank_g};
   if (!shape_ok(sh) || proj_stride < sh.row()) return EK_ERR_ARG;
-  const size_t smem = (size_t)(2 * sh.cq() + rank_a) * sizeof(float);
+  const size_t smem = (size_t)(2 * sh.cq()) * sizeof(float);
   if (smem > 200 * 1024) return EK_ERR_ARG;
   if (smem > 40 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  delta_prepare_kernel<<<n_tokens, 256, smem, stream>>>(qn, kn, vc, beta, decay, proj, proj_stride, conv_w,
-                                                        a2t, dt_bias, a_log, state, (size_t)slot_stride,
+  delta_prepare_kernel<<<n_tokens, 256, smem, stream>>>(qn, kn, vc, beta, proj, proj_stride, conv_w,
+                                                        state, (size_t)slot_stride,
                                                         (size_t)tail_offset, positions, token_slot, sh);
   EK_RETURN_LAUNCH_STATUS();
 }
@@ -317,7 +405,8 @@ EK_EXPORT int ek_delta_conv_tail(float* state, long long slot_stride, long long 
                                  int taps, cudaStream_t stream) {
   if (n_seqs <= 0 || taps <= 1) return 0;
   if (channels <= 0 || proj_stride < channels) return EK_ERR_ARG;
-  ek::delta_conv_tail_kernel<<<n_seqs, 256, 0, stream>>>(state, (size_t)slot_stride, (size_t)tail_offset,
+  dim3 grid(n_seqs, (channels + 255) / 256 > 64 ? 64 : (channels + 255) / 256);
+  ek::delta_conv_tail_kernel<<<grid, 256, 0, stream>>>(state, (size_t)slot_stride, (size_t)tail_offset,
                                                          proj, proj_stride, cu_seqlens, positions,
                                                          token_slot, channels, taps);
   EK_RETURN_LAUNCH_STATUS();
@@ -336,31 +425,29 @@ EK_EXPORT int ek_delta_scan(float* out, const float* qn, const float* kn, const 
   if (grid.z > 65535) return EK_ERR_ARG;
   const int rows = ek_delta_state_rows(dim);
 #define EK_SCAN(RPL)                                                                                 \
-  delta_scan_kernel<RPL><<<grid, kScanCols * kScanLanes, 0, stream>>>(                               \
-      out, qn, kn, vc, beta, decay, state, (size_t)slot_stride, cu_seqlens, positions, token_slot, sh)
+  return (int)launch_scan<RPL>(grid, stream, out, qn, kn, vc, beta, decay, state, (size_t)slot_stride, \
+                               cu_seqlens, positions, token_slot, sh)
   switch (rows) {
-    case 32: EK_SCAN(4); break;
-    case 64: EK_SCAN(8); break;
-    case 128: EK_SCAN(16); break;
-    case 256: EK_SCAN(32); break;
+    case 32: EK_SCAN(4);
+    case 64: EK_SCAN(8);
+    case 128: EK_SCAN(16);
+    case 256: EK_SCAN(32);
     default: return EK_ERR_ARG;
   }
 #undef EK_SCAN
-  EK_RETURN_LAUNCH_STATUS();
 }
 
 #define EK_INSTANTIATE(SUFFIX, T)                                                                    \
-  EK_EXPORT int ek_delta_out_norm_##SUFFIX(void* y, const float* o, const float* proj, int proj_stride, \
-                                           const float* g2t, const float* w, float eps,              \
+  EK_EXPORT int ek_delta_out_norm_##SUFFIX(void* y, const float* o, const float* gate,                \
+                                           const float* w, float eps,                                \
                                            const int* positions, int n_tokens, int heads,            \
                                            int kv_heads, int dim, int vdim, int taps, int rank_a,    \
                                            int rank_g, cudaStream_t stream) {                        \
     using namespace ek;                                                                              \
     if (n_tokens <= 0) return 0;                                                                     \
     DeltaShape sh{heads, kv_heads, dim, vdim, taps, rank_a, rank_g};                                 \
-    if (!shape_ok(sh) || proj_stride < sh.row() || rank_g > 8192) return EK_ERR_ARG;                 \
-    delta_out_norm_kernel<T><<<n_tokens, 256, rank_g * sizeof(float), stream>>>(                     \
-        (T*)y, o, proj, proj_stride, g2t, w, eps, positions, sh);                                    \
+    if (!shape_ok(sh)) return EK_ERR_ARG;                                                            \
+    delta_out_norm_kernel<T><<<n_tokens, 256, 0, stream>>>((T*)y, o, gate, w, eps, positions, sh);   \
     EK_RETURN_LAUNCH_STATUS();                                                                       \
   }
 

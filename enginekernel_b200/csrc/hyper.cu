@@ -52,34 +52,62 @@ __global__ void hc_step_kernel(float* __restrict__ streams, const T* __restrict_
   __syncthreads();
   const size_t t = blockIdx.x;
   float* xs = streams + t * n * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float x[kMaxStreams];
+  // V values a thread and step: four (16-byte accesses) when rows allow, else one
+  const int V = (width % 4 == 0) ? 4 : 1;
+  for (int i0 = threadIdx.x * V; i0 < width; i0 += blockDim.x * V) {
+    float x[kMaxStreams][4];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) x[s] = s < n ? xs[(size_t)s * width + i] : 0.f;
+    for (int s = 0; s < kMaxStreams; ++s) {
+      if (s < n) {
+        if (V == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)s * width + i0);
+          x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
+        } else {
+          x[s][0] = xs[(size_t)s * width + i0];
+          x[s][1] = x[s][2] = x[s][3] = 0.f;
+        }
+      } else {
+        x[s][0] = x[s][1] = x[s][2] = x[s][3] = 0.f;
+      }
+    }
     if (y != nullptr) {
-      const float yv = to_f<T>(y[t * width + i]);
-      float nx[kMaxStreams];
+      float yv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (V == 4) {
+        const float4 v = Vec4<T>::load(y + t * width + i0);
+        yv[0] = v.x; yv[1] = v.y; yv[2] = v.z; yv[3] = v.w;
+      } else {
+        yv[0] = to_f<T>(y[t * width + i0]);
+      }
+      float nx[kMaxStreams][4];
 #pragma unroll
       for (int to = 0; to < kMaxStreams; ++to) {
-        float a = 0.f;
-        if (to < n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a = 0.f;
 #pragma unroll
           for (int s = 0; s < kMaxStreams; ++s)
-            if (s < n) a += c.mix[s * n + to] * x[s];
-          a += c.out[to] * yv;
-          xs[(size_t)to * width + i] = a;
+            if (s < n && to < n) a += c.mix[s * n + to] * x[s][j];
+          nx[to][j] = to < n ? a + c.out[to] * yv[j] : 0.f;
         }
-        nx[to] = a;
+        if (to < n) {
+          if (V == 4) *reinterpret_cast<float4*>(xs + (size_t)to * width + i0) = make_float4(nx[to][0], nx[to][1], nx[to][2], nx[to][3]);
+          else xs[(size_t)to * width + i0] = nx[to][0];
+        }
       }
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s) x[s] = nx[s];
+      for (int s = 0; s < kMaxStreams; ++s)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[s][j] = nx[s][j];
     }
     if (u != nullptr) {
-      float a = 0.f;
+      float a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int s = 0; s < kMaxStreams; ++s)
-        if (s < n) a += c.in[s] * x[s];
-      u[t * width + i] = a;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (s < n) a[j] += c.in[s] * x[s][j];
+      if (V == 4) *reinterpret_cast<float4*>(u + t * width + i0) = make_float4(a[0], a[1], a[2], a[3]);
+      else u[t * width + i0] = a[0];
     }
   }
 }

@@ -101,6 +101,7 @@ head_linear_kernel(T* __restrict__ out, int out_row_stride, int out_head_stride,
 #pragma unroll
     for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = 0.f;
     const T* wp = w + (size_t)h * n_in * n_out + o;
+#pragma unroll 8
     for (int i = 0; i < n_in; ++i) {
       const float wv = to_f<T>(wp[(size_t)i * n_out]);
 #pragma unroll

@@ -227,8 +227,9 @@ moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, cons
 
 // ---------------------------------------------------------------------------------------------
 // The same product on the tensor cores (bfloat16 operands, 32-bit accumulators): a block takes a
-// 64-row tile of the plan and 128 columns, eight warps of 32 x 32 each, K in steps of 32 through
-// shared memory (rows padded by 16 bytes: ldmatrix without bank conflicts).  K % 8 == 0.
+// 64-row tile of the plan and 128 columns, eight warps of 32 x 32 each, K in steps of 32 through a
+// ring of three shared-memory stages filled by cp.async (rows padded by 16 bytes: ldmatrix without
+// bank conflicts).  K % 8 == 0.
 __device__ __forceinline__ void ldsm_x4(uint32_t r[4], const bf16* p) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -242,15 +243,26 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 16 bytes global -> shared without passing through registers; `bytes` = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, int bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 template <bool UP>
 __global__ void __launch_bounds__(256)
 moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a, const bf16* __restrict__ w,
                              const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                              const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
                              int top, int N, int K, int act) {
-  constexpr int BM = kTileRows, BN = 128, BK = 32, LD = BK + 8;
-  __shared__ __align__(16) bf16 As[BM][LD];
-  __shared__ __align__(16) bf16 Ws[BN][LD];
+  constexpr int BM = kTileRows, BN = 128, BK = 32, LD = BK + 8, STAGES = 3;
+  __shared__ __align__(16) bf16 As[STAGES][BM][LD];
+  __shared__ __align__(16) bf16 Ws[STAGES][BN][LD];
   __shared__ int src_row[BM];
   __shared__ int pair_s[BM];
   pdl_launch_dependents();
@@ -274,40 +286,56 @@ moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    {                                            // A: 64 rows x 4 chunks of 8 values
-      const int row = tid >> 2, ch = tid & 3;
-      const int src = src_row[row], gk = k0 + ch * 8;
-      const uint4 v = (src >= 0 && gk < K) ? *reinterpret_cast<const uint4*>(a + (size_t)src * K + gk) : zero;
-      *reinterpret_cast<uint4*>(&As[row][ch * 8]) = v;
-    }
+
+  // a thread's copies of a K step: one 16-byte piece of A (64 rows x 4 pieces), two of W (128 x 4)
+  const int a_row = tid >> 2, piece = tid & 3;
+  const int a_src = src_row[a_row];
+  const bf16* a_from = a + (size_t)(a_src < 0 ? 0 : a_src) * K + piece * 8;
+  const bf16* w_from[2];
+  bool w_ok[2];
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {             // W: 128 rows x 4 chunks
-      const int idx = tid + it * 256;
-      const int row = idx >> 2, ch = idx & 3;
-      const int gn = n0 + row, gk = k0 + ch * 8;
-      const uint4 v = (gn < N && gk < K) ? *reinterpret_cast<const uint4*>(we + (size_t)gn * K + gk) : zero;
-      *reinterpret_cast<uint4*>(&Ws[row][ch * 8]) = v;
-    }
-    __syncthreads();
+  for (int it = 0; it < 2; ++it) {
+    const int gn = n0 + a_row + it * 64;
+    w_ok[it] = gn < N;
+    w_from[it] = we + (size_t)(w_ok[it] ? gn : 0) * K + piece * 8;
+  }
+  auto load = [&](int stage, int kt) {
+    const int k0 = kt * BK;
+    const bool in_k = k0 + piece * 8 < K;
+    cp_async_16(&As[stage][a_row][piece * 8], in_k ? a_from + k0 : a, (a_src >= 0 && in_k) ? 16 : 0);
+#pragma unroll
+    for (int it = 0; it < 2; ++it)
+      cp_async_16(&Ws[stage][a_row + it * 64][piece * 8], in_k ? w_from[it] + k0 : w, (w_ok[it] && in_k) ? 16 : 0);
+  };
+  const int KT = (K + BK - 1) / BK;
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < KT) load(st, st);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < KT; ++kt) {
+    cp_async_wait_group<STAGES - 2>();           // this step's tiles have landed
+    __syncthreads();                             // ... for everyone, and the stage refilled below is free
+    if (kt + STAGES - 1 < KT) load((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
+    cp_async_commit();
+    const int st = kt % STAGES;
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t af[2][4], bfr[2][4];
 #pragma unroll
       for (int i = 0; i < 2; ++i)                // rows (lane % 16), k half (lane / 16)
-        ldsm_x4(af[i], &As[wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+        ldsm_x4(af[i], &As[st][wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
       for (int j = 0; j < 2; ++j)                // two n8 tiles a load: n = (lane / 16) * 8 + lane % 8, k half (lane / 8) % 2
-        ldsm_x4(bfr[j], &Ws[wn * 32 + j * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+        ldsm_x4(bfr[j], &Ws[st][wn * 32 + j * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           mma_bf16_16816(acc[i][j], af[i], bfr[j >> 1][(j & 1) * 2], bfr[j >> 1][(j & 1) * 2 + 1]);
     }
-    __syncthreads();
   }
+  cp_async_wait_group<0>();
   const int g = lane >> 2, tq = lane & 3;
 #pragma unroll
   for (int i = 0; i < 2; ++i)

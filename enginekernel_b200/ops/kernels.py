@@ -1057,14 +1057,16 @@ def head_linear(out, x, w, n_tokens, heads, n_in, n_out, rot=None):
 # ------------------------------------------------------------------ delta rule with a decay per key channel
 _delta_state_rows = Function("delta", "ek_delta_state_rows", [c_int], check_status=False)
 _delta_prepare = Function("delta", "ek_delta_prepare",
-                          [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, c_longlong, c_longlong, _P, _P,
+                          [_P, _P, _P, _P, _P, c_int, _P, _P, c_longlong, c_longlong, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P])
+_delta_low_rank = Function("delta", "ek_delta_low_rank",
+                           [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, _P])
 _delta_conv_tail = Function("delta", "ek_delta_conv_tail",
                             [_P, c_longlong, c_longlong, _P, c_int, _P, _P, _P, c_int, c_int, c_int, _P])
 _delta_scan = Function("delta", "ek_delta_scan",
                        [_P, _P, _P, _P, _P, _P, _P, c_longlong, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
 _delta_out_norm = _per_dtype("delta", "ek_delta_out_norm",
-                             [_P, _P, _P, c_int, _P, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                             [_P, _P, _P, _P, c_float, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, _P])
 DELTA_MAX_KEY_DIM = 256
 
@@ -1079,18 +1081,32 @@ def delta_state_rows(dim: int) -> int:
             return rows
 
 
-def delta_prepare(qn, kn, vc, beta, decay, proj, n_tokens, conv_w, a2t, dt_bias, a_log, state, tail_offset,
-                  positions, token_slot, shape):
+def delta_low_rank(out, proj, n_tokens, offset, w2t, bias=None, a_log=None, dim=1):
+    """The second half of a low-rank pair for every token: out[t, c] = f(bias[c] + sum_r w2t[r, c] *
+    proj[t, offset + r]), all 32-bit.  With ``a_log`` [heads] (a head is ``dim`` neighbouring channels) f is
+    the decay exp(-exp(a_log) * softplus(.)); without, the sigmoid."""
+    _need_cuda(out, proj, w2t, bias, a_log)
+    for t in (out, proj, w2t, bias, a_log):
+        _need(t is None or (t.dtype == torch.float32 and t.stride(-1) == 1), "delta_low_rank: 32-bit tensors")
+    rank, channels = w2t.shape
+    _need(w2t.is_contiguous() and out.is_contiguous() and out.shape[-1] == channels, "delta_low_rank: w2t [rank, channels]")
+    if lib.recording():
+        lib.annotate(bytes=4 * (n_tokens * (rank + channels) + rank * channels), flops=2 * n_tokens * rank * channels)
+    _delta_low_rank(_ptr(out), _ptr(proj), proj.stride(0), offset, rank, _ptr(w2t), _ptr(bias), _ptr(a_log), dim,
+                    channels, n_tokens, 0 if a_log is not None else 1, _stream())
+
+
+def delta_prepare(qn, kn, vc, beta, proj, n_tokens, conv_w, state, tail_offset, positions, token_slot, shape):
     """``shape`` = (heads, kv_heads, dim, vdim, taps, rank_a, rank_g).  ``proj`` [T, q|k|v|beta|a1|g1] in
     32-bit; ``state`` [slots, values] 32-bit with the convolution's last inputs from ``tail_offset`` on.
-    Writes the unit q and k, the convolved v, beta and the decays (all 32-bit)."""
-    _need_cuda(qn, kn, vc, beta, decay, proj, conv_w, a2t, dt_bias, a_log, state, positions, token_slot)
-    for t in (qn, kn, vc, beta, decay, proj, conv_w, a2t, dt_bias, a_log, state):
+    Writes the unit q and k, the convolved v and beta (all 32-bit)."""
+    _need_cuda(qn, kn, vc, beta, proj, conv_w, state, positions, token_slot)
+    for t in (qn, kn, vc, beta, proj, conv_w, state):
         _need(t.dtype == torch.float32 and t.stride(-1) == 1, "delta_prepare: 32-bit tensors")
     if lib.recording():
-        lib.annotate(bytes=4 * n_tokens * (proj.shape[-1] + 2 * qn.shape[-1] + vc.shape[-1] + decay.shape[-1]))
-    _delta_prepare(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(decay), _ptr(proj), proj.stride(0),
-                   _ptr(conv_w), _ptr(a2t), _ptr(dt_bias), _ptr(a_log), _ptr(state), state.stride(0),
+        lib.annotate(bytes=4 * n_tokens * (proj.shape[-1] + 2 * qn.shape[-1] + vc.shape[-1]))
+    _delta_prepare(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(proj), proj.stride(0),
+                   _ptr(conv_w), _ptr(state), state.stride(0),
                    tail_offset, _ptr(positions), _ptr(token_slot), n_tokens, *[int(v) for v in shape], _stream())
 
 
@@ -1115,14 +1131,14 @@ def delta_scan(out, qn, kn, vc, beta, decay, state, cu_seqlens, positions, token
                 _stream())
 
 
-def delta_out_norm(y, o, proj, g2t, w, eps, positions, n_tokens, shape):
-    """y = o / rms(o) per head * w * sigmoid(g2 . g1) in the activation type."""
-    _need_cuda(y, o, proj, g2t, w, positions)
-    _need(o.dtype == proj.dtype == g2t.dtype == w.dtype == torch.float32 and y.is_contiguous() and o.is_contiguous(),
-          "delta_out_norm: 32-bit inputs")
+def delta_out_norm(y, o, gate, w, eps, positions, n_tokens, shape):
+    """y = o / rms(o) per head * w * gate in the activation type (``o``, ``gate`` [T, heads * vdim] 32-bit)."""
+    _need_cuda(y, o, gate, w, positions)
+    _need(o.dtype == gate.dtype == w.dtype == torch.float32 and y.is_contiguous() and o.is_contiguous()
+          and gate.is_contiguous(), "delta_out_norm: 32-bit inputs")
     if lib.recording():
-        lib.annotate(bytes=n_tokens * o.shape[-1] * (4 + y.element_size()) + 4 * g2t.numel())
-    _delta_out_norm[y.dtype](_ptr(y), _ptr(o), _ptr(proj), proj.stride(0), _ptr(g2t), _ptr(w), float(eps),
+        lib.annotate(bytes=n_tokens * o.shape[-1] * (8 + y.element_size()))
+    _delta_out_norm[y.dtype](_ptr(y), _ptr(o), _ptr(gate), _ptr(w), float(eps),
                              _ptr(positions), n_tokens, *[int(v) for v in shape], _stream())
 
 

@@ -102,8 +102,12 @@ class ChannelDelta(Mixer):
         vc = ws.get("delta_v", (t, nh * e), f32)
         beta = ws.get("delta_beta", (t, nh), f32)
         decay = ws.get("delta_decay", (t, nh * d), f32)
-        kernels.delta_prepare(qn, kn, vc, beta, decay, proj, t, self.conv_w, self.a2t, self.dt_bias, self.a_log,
-                              state, self.s_values, ctx.positions, ctx.token_slot, self.shape())
+        gate = ws.get("delta_gate", (t, nh * e), f32)
+        off_a = self.channels + nh
+        kernels.delta_low_rank(decay, proj, t, off_a, self.a2t, bias=self.dt_bias, a_log=self.a_log, dim=d)
+        kernels.delta_low_rank(gate, proj, t, off_a + self.rank_a, self.g2t)
+        kernels.delta_prepare(qn, kn, vc, beta, proj, t, self.conv_w, state, self.s_values, ctx.positions,
+                              ctx.token_slot, self.shape())
         if writes_cache:
             kernels.delta_conv_tail(state, self.s_values, proj, ctx.cu_seqlens, ctx.positions, ctx.token_slot,
                                     ctx.n_seqs, self.channels, self.taps)
@@ -111,5 +115,5 @@ class ChannelDelta(Mixer):
         kernels.delta_scan(o, qn, kn, vc, beta, decay, state, ctx.cu_seqlens, ctx.positions, ctx.token_slot,
                            ctx.n_seqs, nh, g, d, e, n_tokens=t)
         y = ws.get("attn_out", (t, nh * e), self.dtype)
-        kernels.delta_out_norm(y, o, proj, self.g2t, self.norm_w, self.eps, ctx.positions, t, self.shape())
+        kernels.delta_out_norm(y, o, gate, self.norm_w, self.eps, ctx.positions, t, self.shape())
         return linear(y, self.w_o, ctx, "attn_proj", n_rows=t)
