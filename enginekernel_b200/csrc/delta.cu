@@ -11,7 +11,7 @@
 // Five kernels, all taking packed rows of several sequences (prompts, chunks, single tokens):
 //   delta_low_rank   the second halves of the two low-rank pairs: decays and output gates, a tile of
 //                    tokens x channels a block so that a weight is fetched once for 16 tokens
-//   delta_prepare    convolution + SiLU, unit norms, beta                        (a block a token)
+//   delta_prepare    convolution + SiLU, unit norms, beta             (a block a token and key head)
 //   delta_conv_tail  the last taps-1 convolution inputs of every sequence -> its state
 //   delta_scan       the recurrence; reads and writes S in the state
 //   delta_out_norm   o / rms(o) * w * gate per head, to the activation type
@@ -45,14 +45,15 @@ __global__ void __launch_bounds__(128)
 delta_low_rank_kernel(float* __restrict__ out, const float* __restrict__ proj, int proj_stride, int offset,
                       int rank, const float* __restrict__ w2t, const float* __restrict__ bias,
                       const float* __restrict__ a_log, int dim, int channels, int n_tokens, int mode) {
-  extern __shared__ float x_s[];                // [kRankTokens][rank]
+  extern __shared__ __align__(16) float x_s[];  // [kRankTokens][ld], ld = rank rounded up to 4
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * kRankTokens, tid = threadIdx.x;
   const int nt = min(kRankTokens, n_tokens - t0);
+  const int ld = (rank + 3) & ~3;
   for (int idx = tid; idx < kRankTokens * rank; idx += blockDim.x) {
     const int tt = idx / rank, r = idx % rank;
-    x_s[idx] = tt < nt ? proj[(size_t)(t0 + tt) * proj_stride + offset + r] : 0.f;
+    x_s[tt * ld + r] = tt < nt ? proj[(size_t)(t0 + tt) * proj_stride + offset + r] : 0.f;
   }
   __syncthreads();
   const int c = blockIdx.y * 128 + tid;
@@ -61,35 +62,46 @@ delta_low_rank_kernel(float* __restrict__ out, const float* __restrict__ proj, i
   const float b = bias ? bias[c] : 0.f;
 #pragma unroll
   for (int tt = 0; tt < kRankTokens; ++tt) acc[tt] = b;
-#pragma unroll 8
-  for (int r = 0; r < rank; ++r) {
+  int r = 0;
+  for (; r + 4 <= rank; r += 4) {               // four weights, then one 16-byte read of a token's four inputs
+    const float w0 = w2t[(size_t)r * channels + c], w1 = w2t[(size_t)(r + 1) * channels + c];
+    const float w2 = w2t[(size_t)(r + 2) * channels + c], w3 = w2t[(size_t)(r + 3) * channels + c];
+#pragma unroll
+    for (int tt = 0; tt < kRankTokens; ++tt) {
+      const float4 x = *reinterpret_cast<const float4*>(x_s + tt * ld + r);
+      acc[tt] = fmaf(w3, x.w, fmaf(w2, x.z, fmaf(w1, x.y, fmaf(w0, x.x, acc[tt]))));
+    }
+  }
+  for (; r < rank; ++r) {
     const float wv = w2t[(size_t)r * channels + c];
 #pragma unroll
-    for (int tt = 0; tt < kRankTokens; ++tt) acc[tt] = fmaf(wv, x_s[tt * rank + r], acc[tt]);
+    for (int tt = 0; tt < kRankTokens; ++tt) acc[tt] = fmaf(wv, x_s[tt * ld + r], acc[tt]);
   }
   const float rate = mode == 0 ? expf(a_log[c / dim]) : 0.f;
   for (int tt = 0; tt < nt; ++tt)
     out[(size_t)(t0 + tt) * channels + c] = mode == 0 ? expf(-rate * softplus_f(acc[tt])) : sigmoid_f(acc[tt]);
 }
 
-// grid: tokens.  proj [T, >= row()] 32-bit.  conv_w [channels][taps] (last column: the current
+// grid (tokens, key heads): a block convolves one q head, one k head and the v channels of the value
+// heads that read them.  proj [T, >= row()] 32-bit.  conv_w [channels][taps] (last column: the current
 // token).  Outputs (32-bit): qn, kn [T, kv_heads * dim]; vc [T, heads * vdim]; beta [T, heads].
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
                      float* __restrict__ beta,
                      const float* __restrict__ proj, int proj_stride, const float* __restrict__ conv_w,
                      const float* __restrict__ state,
                      size_t slot_stride, size_t tail_offset, const int* __restrict__ positions,
                      const int* __restrict__ token_slot, DeltaShape sh) {
-  extern __shared__ float qk_s[];               // [2 * cq] convolved q and k
+  extern __shared__ float qk_s[];               // [2][dim] convolved q and k of this key head
   __shared__ int n_prev_s;
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, tid = threadIdx.x;
+  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
   const int pos = positions[t];
   if (pos < 0) return;
   const int slot = token_slot[t];
-  const int K = sh.taps, cq = sh.cq(), nch = sh.channels();
+  const int K = sh.taps, cq = sh.cq(), rep = sh.heads / sh.kv_heads;
   if (tid == 0) {
     int n = 0;                                  // predecessors of this token inside the step
     while (n < K - 1 && t - n - 1 >= 0 && token_slot[t - n - 1] == slot && positions[t - n - 1] == pos - n - 1) ++n;
@@ -99,7 +111,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
   __syncthreads();
   const int n_prev = n_prev_s;
   const float* tail = state + (size_t)slot * slot_stride + tail_offset;
-  for (int c = tid; c < nch; c += blockDim.x) {
+  auto convolve = [&](int c) {                  // channel c of [q | k | v]: convolution, then SiLU
     const float* w = conv_w + (size_t)c * K;
     float acc = w[K - 1] * row[c];
     for (int j = 1; j < K; ++j) {
@@ -107,26 +119,26 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
                                   : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
       acc = fmaf(w[K - 1 - j], x, acc);
     }
-    const float y = acc * sigmoid_f(acc);
-    if (c < 2 * cq) qk_s[c] = y;
-    else vc[(size_t)t * sh.cv() + (c - 2 * cq)] = y;
-  }
-  __syncthreads();
-  // unit vectors per head: a warp a head
-  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-  const float q_scale = rsqrtf((float)sh.dim);
-  for (int hh = warp; hh < 2 * sh.kv_heads; hh += nwarps) {
-    const float* x = qk_s + (size_t)hh * sh.dim;
-    float ss = 0.f;
-    for (int i = lane; i < sh.dim; i += 32) ss += x[i] * x[i];
-    ss = warp_sum(ss);
-    const bool is_q = hh < sh.kv_heads;
-    const float f = rsqrtf(ss + 1e-6f) * (is_q ? q_scale : 1.f);
-    float* dst = (is_q ? qn : kn) + (size_t)t * cq + (size_t)(is_q ? hh : hh - sh.kv_heads) * sh.dim;
-    for (int i = lane; i < sh.dim; i += 32) dst[i] = x[i] * f;
-  }
-  for (int h = tid; h < sh.heads; h += blockDim.x)
+    return acc * sigmoid_f(acc);
+  };
+  for (int i = tid; i < 2 * sh.dim; i += blockDim.x)
+    qk_s[i] = convolve((i < sh.dim ? 0 : cq - sh.dim) + g * sh.dim + i);      // q head g, then k head g
+  const int v0 = g * rep * sh.vdim;             // this key head's value channels
+  for (int i = tid; i < rep * sh.vdim; i += blockDim.x)
+    vc[(size_t)t * sh.cv() + v0 + i] = convolve(2 * cq + v0 + i);
+  for (int h = g * rep + tid; h < (g + 1) * rep; h += blockDim.x)
     beta[(size_t)t * sh.heads + h] = sigmoid_f(row[sh.off_beta() + h]);
+  __syncthreads();
+  // unit vectors: q (also times dim^-1/2), then k
+  for (int which = 0; which < 2; ++which) {
+    const float* x = qk_s + which * sh.dim;
+    float ss = 0.f;
+    for (int i = tid; i < sh.dim; i += blockDim.x) ss += x[i] * x[i];
+    ss = block_sum(ss, scratch);
+    const float f = rsqrtf(ss + 1e-6f) * (which == 0 ? rsqrtf((float)sh.dim) : 1.f);
+    float* dst = (which == 0 ? qn : kn) + (size_t)t * cq + (size_t)g * sh.dim;
+    for (int i = tid; i < sh.dim; i += blockDim.x) dst[i] = x[i] * f;
+  }
 }
 
 // grid (sequences, channel tiles).  After the step the state's tail holds the last taps-1 inputs of the sequence.
@@ -150,12 +162,13 @@ __global__ void delta_conv_tail_kernel(float* __restrict__ state, size_t slot_st
   }
 }
 
-constexpr int kScanCols = 32;        // columns of S a block takes
+constexpr int kScanCols = 16;        // columns of S a block takes
 constexpr int kScanLanes = 8;        // lanes that share a column
 constexpr int kScanChunk = 16;       // tokens fetched into shared memory at a time
 constexpr int kScanThreads = kScanCols * kScanLanes;
 
-// grid (sequences, heads, column tiles); 256 threads = 32 columns x 8 lanes; a lane holds RPL
+// grid (sequences, heads, column tiles); 128 threads = 16 columns x 8 lanes (small blocks: the scan is a
+// chain of latencies, and more blocks put it on more SMs); a lane holds RPL
 // consecutive rows of its column.  The tokens' q, k, decays, v and beta come in chunks of 16 through
 // two shared-memory buffers: while a chunk is worked through, the next one is on its way from global
 // memory into registers and is put down behind the chunk's last token.  Only S^T k lies on the chain
@@ -367,7 +380,7 @@ EK_EXPORT int ek_delta_low_rank(float* out, const float* proj, int proj_stride, 
       (mode == 0 && !a_log) || (channels + 127) / 128 > 65535)
     return EK_ERR_ARG;
   dim3 grid((n_tokens + kRankTokens - 1) / kRankTokens, (channels + 127) / 128);
-  const size_t smem = (size_t)kRankTokens * rank * sizeof(float);
+  const size_t smem = (size_t)kRankTokens * ((rank + 3) & ~3) * sizeof(float);
   if (smem > 40 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_low_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -386,14 +399,9 @@ EK_EXPORT int ek_delta_prepare(float* qn, float* kn, float* vc, float* beta,
   if (n_tokens <= 0) return 0;
   DeltaShape sh{heads, kv_heads, dim, vdim, taps, rank_a, rank_g};
   if (!shape_ok(sh) || proj_stride < sh.row()) return EK_ERR_ARG;
-  const size_t smem = (size_t)(2 * sh.cq()) * sizeof(float);
-  if (smem > 200 * 1024) return EK_ERR_ARG;
-  if (smem > 40 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
-  delta_prepare_kernel<<<n_tokens, 256, smem, stream>>>(qn, kn, vc, beta, proj, proj_stride, conv_w,
+  const size_t smem = (size_t)(2 * dim) * sizeof(float);
+  if (smem > 40 * 1024 || kv_heads > 65535) return EK_ERR_ARG;
+  delta_prepare_kernel<<<dim3(n_tokens, kv_heads), 128, smem, stream>>>(qn, kn, vc, beta, proj, proj_stride, conv_w,
                                                         state, (size_t)slot_stride,
                                                         (size_t)tail_offset, positions, token_slot, sh);
   EK_RETURN_LAUNCH_STATUS();

@@ -70,13 +70,17 @@ __global__ void latent_prepare_kernel(T* __restrict__ cq, const float* __restric
 }
 
 constexpr int kHeadTokens = 8;       // tokens a block of the per-head products takes
-constexpr int kHeadThreads = 128;    // = output values a block takes
+constexpr int kHeadOuts = 32;        // output values a block takes ...
+constexpr int kHeadSlices = 4;       // ... each summed by this many threads over a quarter of the inputs
+constexpr int kHeadThreads = kHeadOuts * kHeadSlices;
 
 // out[t, h, o] = sum_i w[h, i, o] * in[t, h, i]   for o < n_out, i < n_in.
-// w is laid out [heads, n_in, n_out] (neighbouring threads read neighbouring weights).
-// grid (token tiles, heads, output tiles).  If rot_dims >= 0 the block with blockIdx.z == 0 also
-// writes the rotated tail: out[t, h, n_out + i] = rot(in[t, h, n_in + i]) for i < R and zeros up to
-// out_head_stride (the absorbed query).
+// w is laid out [heads, n_in, n_out] (neighbouring threads read neighbouring weights); w == null
+// skips the product.  grid (token tiles, heads, output tiles of 32); a warp takes a quarter of the
+// inputs for the tile's 32 outputs and the four warps' sums meet in shared memory, so that with few
+// tokens the chain of loads is short and the weights are spread over many blocks.  If rot_dims >= 0
+// the block with blockIdx.z == 0 also writes the rotated tail: out[t, h, n_out + i] =
+// rot(in[t, h, n_in + i]) for i < R and zeros up to out_head_stride (the absorbed query).
 template <typename T>
 __global__ void __launch_bounds__(kHeadThreads)
 head_linear_kernel(T* __restrict__ out, int out_row_stride, int out_head_stride,
@@ -85,6 +89,7 @@ head_linear_kernel(T* __restrict__ out, int out_row_stride, int out_head_stride,
                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                    const int* __restrict__ positions) {
   extern __shared__ float in_s[];               // [kHeadTokens][n_in + R]
+  __shared__ float part_s[kHeadSlices][kHeadTokens][kHeadOuts];
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * kHeadTokens, h = blockIdx.y, tid = threadIdx.x;
@@ -95,20 +100,35 @@ head_linear_kernel(T* __restrict__ out, int out_row_stride, int out_head_stride,
     in_s[idx] = tt < nt ? to_f<T>(in[(size_t)(t0 + tt) * in_row_stride + (size_t)h * in_head_stride + i]) : 0.f;
   }
   __syncthreads();
-  const int o = blockIdx.z * kHeadThreads + tid;
-  if (o < n_out) {
+  if (w != nullptr) {
+    const int slice = tid / kHeadOuts, oo = tid % kHeadOuts;
+    const int o = blockIdx.z * kHeadOuts + oo;
+    const int per = (n_in + kHeadSlices - 1) / kHeadSlices;
+    const int i0 = slice * per, i1 = min(n_in, i0 + per);
     float acc[kHeadTokens];
 #pragma unroll
     for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = 0.f;
-    const T* wp = w + (size_t)h * n_in * n_out + o;
+    if (o < n_out) {
+      const T* wp = w + (size_t)h * n_in * n_out + o;
 #pragma unroll 8
-    for (int i = 0; i < n_in; ++i) {
-      const float wv = to_f<T>(wp[(size_t)i * n_out]);
+      for (int i = i0; i < i1; ++i) {
+        const float wv = to_f<T>(wp[(size_t)i * n_out]);
 #pragma unroll
-      for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = fmaf(wv, in_s[tt * width + i], acc[tt]);
+        for (int tt = 0; tt < kHeadTokens; ++tt) acc[tt] = fmaf(wv, in_s[tt * width + i], acc[tt]);
+      }
     }
-    for (int tt = 0; tt < nt; ++tt)
-      out[(size_t)(t0 + tt) * out_row_stride + (size_t)h * out_head_stride + o] = from_f<T>(acc[tt]);
+#pragma unroll
+    for (int tt = 0; tt < kHeadTokens; ++tt) part_s[slice][tt][oo] = acc[tt];
+    __syncthreads();
+    for (int idx = tid; idx < nt * kHeadOuts; idx += kHeadThreads) {
+      const int tt = idx / kHeadOuts, o2 = blockIdx.z * kHeadOuts + idx % kHeadOuts;
+      if (o2 < n_out) {
+        float v = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < kHeadSlices; ++sl) v += part_s[sl][tt][idx % kHeadOuts];
+        out[(size_t)(t0 + tt) * out_row_stride + (size_t)h * out_head_stride + o2] = from_f<T>(v);
+      }
+    }
   }
   if (rot_dims >= 0 && blockIdx.z == 0) {
     const int half = rot_dims / 2;
@@ -151,7 +171,8 @@ static int launch_head_linear(T* out, int out_row_stride, int out_head_stride, c
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, heads, (n_out + kHeadThreads - 1) / kHeadThreads);
+  dim3 grid((n_tokens + kHeadTokens - 1) / kHeadTokens, heads, w ? (n_out + kHeadOuts - 1) / kHeadOuts : 1);
+  if (grid.z > 65535) return EK_ERR_ARG;
   head_linear_kernel<T><<<grid, kHeadThreads, smem, stream>>>(
       out, out_row_stride, out_head_stride, in, in_row_stride, in_head_stride, w, n_tokens, n_in, n_out,
       R, rot_dims, cos_t, sin_t, positions);

@@ -227,7 +227,7 @@ moe_expert_product_kernel(void* __restrict__ out_, const T* __restrict__ a, cons
 
 // ---------------------------------------------------------------------------------------------
 // The same product on the tensor cores (bfloat16 operands, 32-bit accumulators): a block takes a
-// 64-row tile of the plan and 128 columns, eight warps of 32 x 32 each, K in steps of 32 through a
+// 64-row tile of the plan and 128 columns, eight warps of 32 x 32 each, K in steps of 64 through a
 // ring of three shared-memory stages filled by cp.async (rows padded by 16 bytes: ldmatrix without
 // bank conflicts).  K % 8 == 0.
 __device__ __forceinline__ void ldsm_x4(uint32_t r[4], const bf16* p) {
@@ -254,15 +254,20 @@ __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+constexpr int kTcCols = 128, kTcK = 64, kTcLd = kTcK + 8, kTcStages = 3;
+constexpr size_t kTcSmem = (size_t)kTcStages * (kTileRows + kTcCols) * kTcLd * sizeof(bf16);
+
 template <bool UP>
 __global__ void __launch_bounds__(256)
 moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a, const bf16* __restrict__ w,
                              const int* __restrict__ tiles, const int* __restrict__ n_tiles,
                              const int* __restrict__ sorted_pair, const float* __restrict__ pair_weight,
                              int top, int N, int K, int act) {
-  constexpr int BM = kTileRows, BN = 128, BK = 32, LD = BK + 8, STAGES = 3;
-  __shared__ __align__(16) bf16 As[STAGES][BM][LD];
-  __shared__ __align__(16) bf16 Ws[STAGES][BN][LD];
+  constexpr int BM = kTileRows, BN = kTcCols, BK = kTcK, LD = kTcLd, STAGES = kTcStages;
+  extern __shared__ __align__(16) unsigned char tc_smem[];
+  typedef bf16 (*Tile)[LD];
+  bf16* const a_base = reinterpret_cast<bf16*>(tc_smem);                  // [STAGES][BM][LD]
+  bf16* const w_base = a_base + STAGES * BM * LD;                          // [STAGES][BN][LD]
   __shared__ int src_row[BM];
   __shared__ int pair_s[BM];
   pdl_launch_dependents();
@@ -287,25 +292,23 @@ moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
 
-  // a thread's copies of a K step: one 16-byte piece of A (64 rows x 4 pieces), two of W (128 x 4)
-  const int a_row = tid >> 2, piece = tid & 3;
-  const int a_src = src_row[a_row];
-  const bf16* a_from = a + (size_t)(a_src < 0 ? 0 : a_src) * K + piece * 8;
-  const bf16* w_from[2];
-  bool w_ok[2];
-#pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    const int gn = n0 + a_row + it * 64;
-    w_ok[it] = gn < N;
-    w_from[it] = we + (size_t)(w_ok[it] ? gn : 0) * K + piece * 8;
-  }
+  // a K step is (64 + 128) rows of 8 pieces of 16 bytes: six pieces a thread
   auto load = [&](int stage, int kt) {
     const int k0 = kt * BK;
-    const bool in_k = k0 + piece * 8 < K;
-    cp_async_16(&As[stage][a_row][piece * 8], in_k ? a_from + k0 : a, (a_src >= 0 && in_k) ? 16 : 0);
 #pragma unroll
-    for (int it = 0; it < 2; ++it)
-      cp_async_16(&Ws[stage][a_row + it * 64][piece * 8], in_k ? w_from[it] + k0 : w, (w_ok[it] && in_k) ? 16 : 0);
+    for (int it = 0; it < (BM + BN) * (BK / 8) / 256; ++it) {
+      const int idx = tid + it * 256, row = idx / (BK / 8), piece = idx % (BK / 8);
+      const int gk = k0 + piece * 8;
+      if (row < BM) {
+        const int src = src_row[row];
+        const bool ok = src >= 0 && gk < K;
+        cp_async_16(a_base + ((size_t)stage * BM + row) * LD + piece * 8, ok ? a + (size_t)src * K + gk : a, ok ? 16 : 0);
+      } else {
+        const int gn = n0 + row - BM;
+        const bool ok = gn < N && gk < K;
+        cp_async_16(w_base + ((size_t)stage * BN + row - BM) * LD + piece * 8, ok ? we + (size_t)gn * K + gk : w, ok ? 16 : 0);
+      }
+    }
   };
   const int KT = (K + BK - 1) / BK;
 #pragma unroll
@@ -319,15 +322,17 @@ moe_expert_product_tc_kernel(void* __restrict__ out_, const bf16* __restrict__ a
     if (kt + STAGES - 1 < KT) load((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
     cp_async_commit();
     const int st = kt % STAGES;
+    Tile As = reinterpret_cast<Tile>(a_base + (size_t)st * BM * LD);
+    Tile Ws = reinterpret_cast<Tile>(w_base + (size_t)st * BN * LD);
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t af[2][4], bfr[2][4];
 #pragma unroll
       for (int i = 0; i < 2; ++i)                // rows (lane % 16), k half (lane / 16)
-        ldsm_x4(af[i], &As[st][wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+        ldsm_x4(af[i], &As[wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
       for (int j = 0; j < 2; ++j)                // two n8 tiles a load: n = (lane / 16) * 8 + lane % 8, k half (lane / 8) % 2
-        ldsm_x4(bfr[j], &Ws[st][wn * 32 + j * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+        ldsm_x4(bfr[j], &Ws[wn * 32 + j * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -412,7 +417,10 @@ EK_EXPORT int ek_moe_expert_up_tc(void* out, const void* x, const void* w, const
   if (N <= 0 || K <= 0 || K % 8 || top <= 0 || (N + 127) / 128 > 65535 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   dim3 grid(max_tiles, (N + 127) / 128);
-  moe_expert_product_tc_kernel<true><<<grid, 256, 0, stream>>>(out, (const bf16*)x, (const bf16*)w, tiles, n_tiles,
+  cudaError_t e = cudaFuncSetAttribute(moe_expert_product_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kTcSmem);
+  if (e != cudaSuccess) return (int)e;
+  moe_expert_product_tc_kernel<true><<<grid, 256, kTcSmem, stream>>>(out, (const bf16*)x, (const bf16*)w, tiles, n_tiles,
                                                               sorted_pair, nullptr, top, N, K, act);
   EK_RETURN_LAUNCH_STATUS();
 }
@@ -425,7 +433,10 @@ EK_EXPORT int ek_moe_expert_down_tc(float* out, const void* a, const void* w, co
   if (N <= 0 || K <= 0 || K % 8 || (N + 127) / 128 > 65535 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
     return EK_ERR_ARG;
   dim3 grid(max_tiles, (N + 127) / 128);
-  moe_expert_product_tc_kernel<false><<<grid, 256, 0, stream>>>(out, (const bf16*)a, (const bf16*)w, tiles, n_tiles,
+  cudaError_t e = cudaFuncSetAttribute(moe_expert_product_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kTcSmem);
+  if (e != cudaSuccess) return (int)e;
+  moe_expert_product_tc_kernel<false><<<grid, 256, kTcSmem, stream>>>(out, (const bf16*)a, (const bf16*)w, tiles, n_tiles,
                                                                sorted_pair, pair_weight, 1, N, K, 0);
   EK_RETURN_LAUNCH_STATUS();
 }

@@ -1031,12 +1031,17 @@ def latent_prepare(cq, proj, n_tokens, gain_q, gain_kv, eps, cos, sin, rot_dims,
                               1 if write_cache else 0, _stream())
 
 
+HEAD_LINEAR_LIBRARY_ROWS = 64     # bfloat16 products per head of more rows than this go to the library
+
+
 def head_linear(out, x, w, n_tokens, heads, n_in, n_out, rot=None):
     """out[t, h, :n_out] = w[h]^T-applied x[t, h, :n_in] for every head: ``w`` is [heads, n_in, n_out],
     ``x`` [T, heads, >= n_in] and ``out`` [T, heads, >= n_out] (any row and head strides, dense
     values).  ``rot=(rot_dim, rot_dims, cos, sin, positions)``: the ``rot_dim`` values behind the
     ``n_in`` of a head are rotated (the first ``rot_dims`` of them, NeoX pairing) and written behind the
-    ``n_out`` results, zeros up to the head's stride."""
+    ``n_out`` results, zeros up to the head's stride.  Many bfloat16 rows (a prompt) go through the
+    library's batched product, as the other products of a prompt may; the kernel then only writes the
+    rotated tail."""
     _need_cuda(out, x, w)
     _need(out.dtype == x.dtype == w.dtype, "head_linear: one dtype")
     _need(out.dim() == 3 and x.dim() == 3 and out.stride(-1) == 1 and x.stride(-1) == 1 and w.is_contiguous()
@@ -1046,10 +1051,23 @@ def head_linear(out, x, w, n_tokens, heads, n_in, n_out, rot=None):
         r, rot_dims, cos, sin, positions = rot
         _need_cuda(cos, sin, positions)
         _need(x.shape[-1] >= n_in + r and out.stride(1) >= n_out + r, "head_linear: room for the rotated tail")
+    by_library = x.dtype == torch.bfloat16 and n_tokens > HEAD_LINEAR_LIBRARY_ROWS
+    if by_library:
+        def product():
+            torch.bmm(x[:n_tokens, :, :n_in].transpose(0, 1), w, out=out[:n_tokens, :, :n_out].transpose(0, 1))
+        product()
+        if lib.recording():
+            lib.record_library_call(f"library_bmm[{heads}x{n_out}x{n_in}]", product,
+                                    bytes=2 * (heads * n_in * n_out + n_tokens * heads * (n_in + n_out)),
+                                    flops=2 * n_tokens * heads * n_in * n_out)
+        if rot is None:
+            return
     if lib.recording():
-        lib.annotate(bytes=x.element_size() * (heads * n_in * n_out + n_tokens * heads * (n_in + n_out + 2 * r)),
-                     flops=2 * n_tokens * heads * n_in * n_out)
-    _head_linear[x.dtype](_ptr(out), out.stride(0), out.stride(1), _ptr(x), x.stride(0), x.stride(1), _ptr(w),
+        lib.annotate(bytes=x.element_size() * ((0 if by_library else heads * n_in * n_out)
+                                               + n_tokens * heads * (n_in + n_out + 2 * r)),
+                     flops=0 if by_library else 2 * n_tokens * heads * n_in * n_out)
+    _head_linear[x.dtype](_ptr(out), out.stride(0), out.stride(1), _ptr(x), x.stride(0), x.stride(1),
+                          None if by_library else _ptr(w),
                           n_tokens, heads, n_in, n_out, r, rot_dims, _ptr(cos), _ptr(sin), _ptr(positions),
                           _stream())
 
