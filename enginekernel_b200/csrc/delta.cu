@@ -78,12 +78,14 @@ delta_low_rank_kernel(float* __restrict__ out, const float* __restrict__ proj, i
     for (int tt = 0; tt < kRankTokens; ++tt) acc[tt] = fmaf(wv, x_s[tt * ld + r], acc[tt]);
   }
   const float rate = mode == 0 ? expf(a_log[c / dim]) : 0.f;
-  for (int tt = 0; tt < nt; ++tt)
-    out[(size_t)(t0 + tt) * channels + c] = mode == 0 ? expf(-rate * softplus_f(acc[tt])) : sigmoid_f(acc[tt]);
+#pragma unroll
+  for (int tt = 0; tt < kRankTokens; ++tt)      // (a fixed trip count keeps acc in registers)
+    if (tt < nt)
+      out[(size_t)(t0 + tt) * channels + c] = mode == 0 ? expf(-rate * softplus_f(acc[tt])) : sigmoid_f(acc[tt]);
 }
 
 // grid (tokens, key heads): a block convolves one q head, one k head and the v channels of the value
-// heads that read them.  proj [T, >= row()] 32-bit.  conv_w [channels][taps] (last column: the current
+// heads that read them (few tokens: many short blocks).  proj [T, >= row()] 32-bit.  conv_w [channels][taps] (last column: the current
 // token).  Outputs (32-bit): qn, kn [T, kv_heads * dim]; vc [T, heads * vdim]; beta [T, heads].
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
@@ -97,7 +99,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
+  const int t = blockIdx.x, tid = threadIdx.x;
   const int pos = positions[t];
   if (pos < 0) return;
   const int slot = token_slot[t];
@@ -121,6 +123,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
     }
     return acc * sigmoid_f(acc);
   };
+  const int g = blockIdx.y;
   for (int i = tid; i < 2 * sh.dim; i += blockDim.x)
     qk_s[i] = convolve((i < sh.dim ? 0 : cq - sh.dim) + g * sh.dim + i);      // q head g, then k head g
   const int v0 = g * rep * sh.vdim;             // this key head's value channels
@@ -139,6 +142,63 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
     float* dst = (which == 0 ? qn : kn) + (size_t)t * cq + (size_t)g * sh.dim;
     for (int i = tid; i < sh.dim; i += blockDim.x) dst[i] = x[i] * f;
   }
+}
+
+// The same with a block a token (many tokens: fewer, longer blocks).  grid: tokens.  proj [T, >= row()] 32-bit.  conv_w [channels][taps] (last column: the current
+// token).  Outputs (32-bit): qn, kn [T, kv_heads * dim]; vc [T, heads * vdim]; beta [T, heads].
+__global__ void __launch_bounds__(256)
+delta_prepare_token_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
+                     float* __restrict__ beta,
+                     const float* __restrict__ proj, int proj_stride, const float* __restrict__ conv_w,
+                     const float* __restrict__ state,
+                     size_t slot_stride, size_t tail_offset, const int* __restrict__ positions,
+                     const int* __restrict__ token_slot, DeltaShape sh) {
+  extern __shared__ float qk_s[];               // [2 * cq] convolved q and k
+  __shared__ int n_prev_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int slot = token_slot[t];
+  const int K = sh.taps, cq = sh.cq(), nch = sh.channels();
+  if (tid == 0) {
+    int n = 0;                                  // predecessors of this token inside the step
+    while (n < K - 1 && t - n - 1 >= 0 && token_slot[t - n - 1] == slot && positions[t - n - 1] == pos - n - 1) ++n;
+    n_prev_s = n;
+  }
+  const float* row = proj + (size_t)t * proj_stride;
+  __syncthreads();
+  const int n_prev = n_prev_s;
+  const float* tail = state + (size_t)slot * slot_stride + tail_offset;
+  for (int c = tid; c < nch; c += blockDim.x) {
+    const float* w = conv_w + (size_t)c * K;
+    float acc = w[K - 1] * row[c];
+    for (int j = 1; j < K; ++j) {
+      const float x = j <= n_prev ? proj[(size_t)(t - j) * proj_stride + c]
+                                  : tail[(size_t)c * (K - 1) + (n_prev - j + K - 1)];
+      acc = fmaf(w[K - 1 - j], x, acc);
+    }
+    const float y = acc * sigmoid_f(acc);
+    if (c < 2 * cq) qk_s[c] = y;
+    else vc[(size_t)t * sh.cv() + (c - 2 * cq)] = y;
+  }
+  __syncthreads();
+  // unit vectors per head: a warp a head
+  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+  const float q_scale = rsqrtf((float)sh.dim);
+  for (int hh = warp; hh < 2 * sh.kv_heads; hh += nwarps) {
+    const float* x = qk_s + (size_t)hh * sh.dim;
+    float ss = 0.f;
+    for (int i = lane; i < sh.dim; i += 32) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const bool is_q = hh < sh.kv_heads;
+    const float f = rsqrtf(ss + 1e-6f) * (is_q ? q_scale : 1.f);
+    float* dst = (is_q ? qn : kn) + (size_t)t * cq + (size_t)(is_q ? hh : hh - sh.kv_heads) * sh.dim;
+    for (int i = lane; i < sh.dim; i += 32) dst[i] = x[i] * f;
+  }
+  for (int h = tid; h < sh.heads; h += blockDim.x)
+    beta[(size_t)t * sh.heads + h] = sigmoid_f(row[sh.off_beta() + h]);
 }
 
 // grid (sequences, channel tiles).  After the step the state's tail holds the last taps-1 inputs of the sequence.
@@ -399,11 +459,24 @@ EK_EXPORT int ek_delta_prepare(float* qn, float* kn, float* vc, float* beta,
   if (n_tokens <= 0) return 0;
   DeltaShape sh{heads, kv_heads, dim, vdim, taps, rank_a, rank_g};
   if (!shape_ok(sh) || proj_stride < sh.row()) return EK_ERR_ARG;
+  if (n_tokens >= 512) {
+    const size_t smem = (size_t)(2 * sh.cq()) * sizeof(float);
+    if (smem > 200 * 1024) return EK_ERR_ARG;
+    if (smem > 40 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(delta_prepare_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    delta_prepare_token_kernel<<<n_tokens, 256, smem, stream>>>(qn, kn, vc, beta, proj, proj_stride, conv_w, state,
+                                                                (size_t)slot_stride, (size_t)tail_offset, positions,
+                                                                token_slot, sh);
+    EK_RETURN_LAUNCH_STATUS();
+  }
   const size_t smem = (size_t)(2 * dim) * sizeof(float);
   if (smem > 40 * 1024 || kv_heads > 65535) return EK_ERR_ARG;
   delta_prepare_kernel<<<dim3(n_tokens, kv_heads), 128, smem, stream>>>(qn, kn, vc, beta, proj, proj_stride, conv_w,
-                                                        state, (size_t)slot_stride,
-                                                        (size_t)tail_offset, positions, token_slot, sh);
+                                                                       state, (size_t)slot_stride,
+                                                                       (size_t)tail_offset, positions, token_slot, sh);
   EK_RETURN_LAUNCH_STATUS();
 }
 
