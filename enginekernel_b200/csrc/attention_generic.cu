@@ -19,6 +19,8 @@
 namespace ek {
 
 constexpr int kAttnThreads = 128;
+constexpr int kGenericMaxDim = 1024;  // this kernel's own limit on the head size: 8 values a thread
+constexpr int kGenericAcc = kGenericMaxDim / kAttnThreads;
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ row, const float* __restrict__ q, int d);
@@ -68,7 +70,7 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          int keys_per_split, float* __restrict__ part_acc,
                                          float* __restrict__ part_ml, float sink,
                                          const float* __restrict__ sinks) {
-  __shared__ float q_s[EK_MAX_HEAD_DIM];
+  __shared__ float q_s[kGenericMaxDim];
   __shared__ float p_s[kAttnThreads];
   __shared__ size_t voff_s[kAttnThreads];
   __shared__ float scratch[33];
@@ -91,7 +93,9 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     }
   }
 
-  float acc0 = 0.f, acc1 = 0.f;                 // dims tid and tid + 128
+  float acc[kGenericAcc];                       // dims tid, tid + 128, ... (those below d)
+#pragma unroll
+  for (int a = 0; a < kGenericAcc; ++a) acc[a] = 0.f;
   float m = -INFINITY, l = 0.f;
   if (hi >= lo) {
     const int slot = token_slot[t];
@@ -116,13 +120,14 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
       l = l * alpha + block_sum(p, scratch);    // the barriers inside also publish p_s, voff_s
       m = m_new;
       const int n = min(kAttnThreads, hi - start + 1);
-      acc0 *= alpha;
-      acc1 *= alpha;
-      if (tid < d) {
-        for (int i = 0; i < n; ++i) acc0 += p_s[i] * to_f<T>(vbase[voff_s[i] + tid]);
-      }
-      if (tid + kAttnThreads < d) {
-        for (int i = 0; i < n; ++i) acc1 += p_s[i] * to_f<T>(vbase[voff_s[i] + tid + kAttnThreads]);
+#pragma unroll
+      for (int a = 0; a < kGenericAcc; ++a) {
+        acc[a] *= alpha;
+        if (tid + a * kAttnThreads < d) {
+          float s2 = acc[a];
+          for (int i = 0; i < n; ++i) s2 += p_s[i] * to_f<T>(vbase[voff_s[i] + tid + a * kAttnThreads]);
+          acc[a] = s2;
+        }
       }
       __syncthreads();                          // before p_s / voff_s are overwritten
     }
@@ -133,12 +138,14 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
     // a sink: one more term exp(sink) in the denominator, with no value (-inf: none)
     if (sink > -INFINITY && l > 0.f) l += expf(sink - m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    if (tid < d) orow[tid] = from_f<T>(acc0 * inv);
-    if (tid + kAttnThreads < d) orow[tid + kAttnThreads] = from_f<T>(acc1 * inv);
+#pragma unroll
+    for (int a = 0; a < kGenericAcc; ++a)
+      if (tid + a * kAttnThreads < d) orow[tid + a * kAttnThreads] = from_f<T>(acc[a] * inv);
   } else {
     float* pa = part_acc + part_index * d;
-    if (tid < d) pa[tid] = acc0;
-    if (tid + kAttnThreads < d) pa[tid + kAttnThreads] = acc1;
+#pragma unroll
+    for (int a = 0; a < kGenericAcc; ++a)
+      if (tid + a * kAttnThreads < d) pa[tid + a * kAttnThreads] = acc[a];
     if (tid == 0) {
       part_ml[2 * part_index] = m;
       part_ml[2 * part_index + 1] = l;
@@ -178,7 +185,7 @@ static int launch(void* out, const void* q, int q_row_stride, const int* positio
                   int keys_per_split, float* part_acc, float* part_ml, float sink,
                   const float* sinks, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (head_dim <= 0 || head_dim > EK_MAX_HEAD_DIM || n_kv_heads <= 0 ||
+  if (head_dim <= 0 || head_dim > kGenericMaxDim || n_kv_heads <= 0 ||
       n_q_heads % n_kv_heads || n_q_heads > 65535 || n_splits < 1 || n_splits > 65535 ||
       (n_splits > 1 && (!part_acc || !part_ml || keys_per_split <= 0)))
     return EK_ERR_ARG;

@@ -19,6 +19,7 @@ from .lib import Function, KernelError, count_extra_launches
 
 PAGE = 64                 # tokens per cache page; must equal EK_PAGE in csrc/common.cuh
 MAX_HEAD_DIM = 256
+GENERIC_MAX_HEAD_DIM = 1024     # the general attention kernel alone takes head sizes up to here
 
 _SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
 _P = c_void_p
@@ -290,7 +291,7 @@ def attention_generic(out, q, n_tokens, positions, token_slot, k_pages, v_pages,
     merged from ``part_acc`` [T, NQ, splits, D] / ``part_ml`` [T, NQ, splits, 2] (32-bit).
     """
     _need_cuda(out, q, positions, token_slot, k_pages, v_pages, block_table, part_acc, part_ml)
-    check_head_dim(head_dim)
+    _need(1 <= head_dim <= GENERIC_MAX_HEAD_DIM, f"attention_generic: head sizes up to {GENERIC_MAX_HEAD_DIM}")
     _need(out.dtype == q.dtype == k_pages.dtype, "attention: one dtype for q, cache and out")
     _need(out.is_contiguous() and out.shape[-1] == n_q_heads * head_dim, "attention: out [T, NQ*D]")
     _need(q.stride(-1) == 1, "attention: q rows must be dense")

@@ -16,7 +16,8 @@ with zeros to the row length D that the attention kernels take, and attention ru
 form: the query of head h becomes [W_uk,h^T q_h,flat ; rot(q_h,rot)] (D values), all H heads read
 the same cached rows as keys AND as values, and W_uv,h is applied to the first c values of each
 head's result.  That is grouped-query attention with one key head, so the framework's attention
-kernels run it (with a sink score per head).
+kernels run it (with a sink score per head): the mma.sync kernels for rows of up to 256 values, the
+general kernel beyond (up to 1,024).
 
 Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (d), ``rot_dim`` (r), ``v_dim`` (e),
 ``q_rank`` (a), ``kv_rank`` (c), ``scale``, ``eps``, ``position`` (a rotary PartSpec over ``rot_dim``
@@ -64,7 +65,9 @@ class LatentAttention(Mixer):
             raise ValueError("latent_attention: the rotation covers more than rot_dim values")
         # the cached row: latent and rotated key part, padded to what every attention kernel takes
         self.row = -(-(self.kv_rank + self.rot_dim) // 32) * 32
-        kernels.check_head_dim(self.row)
+        if self.row > kernels.GENERIC_MAX_HEAD_DIM:
+            raise kernels.KernelError(f"latent_attention: a cached row of {self.row} values (kv_rank + rot_dim) exceeds "
+                                      f"the attention kernels' limit of {kernels.GENERIC_MAX_HEAD_DIM}")
         self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = None
         self.gain_q = self.gain_kv = self.sinks = None
 

@@ -287,6 +287,8 @@ def _one_layer(mixer_entry, width, vocab, streams):
 ONE_LAYER = {
     "latent": _one_layer(models.latent(3, 24, 8, 40, 48, 40, scaling=(4.0, 64, 8.0, 1.0), scale=0.9), 96, 600, 2),
     "latent_wide": _one_layer(models.latent(6, 64, 32, 48, 96, 160, scaling=(8.0, 256, 32.0, 1.0), scale=0.5), 128, 600, None),
+    # a cached row of 304 values: beyond what the mma.sync attention kernels take, so the general kernel runs it
+    "latent_long_row": _one_layer(models.latent(2, 16, 16, 24, 32, 288, scale=0.7), 64, 600, None),
     "delta": _one_layer(models.delta(4, 2, 16, 24, 3, (8, 12)), 96, 83, 3),
     "delta_wide": _one_layer(models.delta(2, 1, 128, 64, 4, (24, 16)), 128, 83, None),
 }
