@@ -3,9 +3,10 @@
 //     u = sum_s in[s] * x_s,
 // and its output y is written back into all of them at once from the old values,
 //     x_t <- sum_s mix[s, t] * x_s + out[t] * y        (mix is indexed [from, to]).
-// One kernel does the write of the sublayer before and the read for the sublayer after, so the
-// streams make one round trip through memory per sublayer.  Everything is computed in 32-bit; y
-// arrives in the activation type T.
+// One kernel does the write of the sublayer before, the read for the sublayer after and the RMS norm
+// of what was read (gain * u * rsqrt(mean(u^2) + eps), the row kept in shared memory meanwhile), so
+// the streams make one round trip through memory per sublayer and the mixture none.  Everything is
+// computed in 32-bit; y arrives, and the normed mixture leaves, in the activation type T.
 #include "common.cuh"
 
 namespace ek {
@@ -33,14 +34,20 @@ __global__ void hc_broadcast_kernel(float* __restrict__ streams, const float* __
 }
 
 // If y != null: the write with (mix, out) of the sublayer before, in place.  Then, if u != null:
-// u[t, :] = sum_s in[s] * x_s.  Coefficient tensors are device pointers ([n], [n], [n, n], 32-bit);
-// any of write_mix / write_out / read_in may be null when the matching half is not asked for.
-template <typename T>
+// u[t, :] = sum_s in[s] * x_s, and if normed != null: normed[t, :] = gain * u / rms(u).  Coefficient
+// tensors are device pointers ([n], [n], [n, n], 32-bit); any of write_mix / write_out / read_in may
+// be null when the matching half is not asked for.
+// NS: the number of streams rounded up to 2, 4 or 8 (the copies a thread holds in registers).
+template <typename T, int NS>
 __global__ void hc_step_kernel(float* __restrict__ streams, const T* __restrict__ y,
                                const float* __restrict__ write_mix, const float* __restrict__ write_out,
                                const float* __restrict__ read_in, float* __restrict__ u, int n,
-                               int width) {
+                               int width, const float* __restrict__ gain, float eps,
+                               T* __restrict__ normed) {
   __shared__ StreamCoefficients c;
+  __shared__ float scratch[33];
+  extern __shared__ __align__(16) float u_s[];  // [width] when the norm is asked for
+  float ss = 0.f;
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x < n) {
@@ -55,9 +62,9 @@ __global__ void hc_step_kernel(float* __restrict__ streams, const T* __restrict_
   // V values a thread and step: four (16-byte accesses) when rows allow, else one
   const int V = (width % 4 == 0) ? 4 : 1;
   for (int i0 = threadIdx.x * V; i0 < width; i0 += blockDim.x * V) {
-    float x[kMaxStreams][4];
+    float x[NS][4];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) {
+    for (int s = 0; s < NS; ++s) {
       if (s < n) {
         if (V == 4) {
           const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)s * width + i0);
@@ -78,14 +85,14 @@ __global__ void hc_step_kernel(float* __restrict__ streams, const T* __restrict_
       } else {
         yv[0] = to_f<T>(y[t * width + i0]);
       }
-      float nx[kMaxStreams][4];
+      float nx[NS][4];
 #pragma unroll
-      for (int to = 0; to < kMaxStreams; ++to) {
+      for (int to = 0; to < NS; ++to) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float a = 0.f;
 #pragma unroll
-          for (int s = 0; s < kMaxStreams; ++s)
+          for (int s = 0; s < NS; ++s)
             if (s < n && to < n) a += c.mix[s * n + to] * x[s][j];
           nx[to][j] = to < n ? a + c.out[to] * yv[j] : 0.f;
         }
@@ -95,20 +102,33 @@ __global__ void hc_step_kernel(float* __restrict__ streams, const T* __restrict_
         }
       }
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
+      for (int s = 0; s < NS; ++s)
 #pragma unroll
         for (int j = 0; j < 4; ++j) x[s][j] = nx[s][j];
     }
-    if (u != nullptr) {
+    if (u != nullptr || normed != nullptr) {
       float a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
+      for (int s = 0; s < NS; ++s)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           if (s < n) a[j] += c.in[s] * x[s][j];
-      if (V == 4) *reinterpret_cast<float4*>(u + t * width + i0) = make_float4(a[0], a[1], a[2], a[3]);
-      else u[t * width + i0] = a[0];
+      if (u != nullptr) {
+        if (V == 4) *reinterpret_cast<float4*>(u + t * width + i0) = make_float4(a[0], a[1], a[2], a[3]);
+        else u[t * width + i0] = a[0];
+      }
+      if (normed != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < V) { u_s[i0 + j] = a[j]; ss += a[j] * a[j]; }
+      }
     }
+  }
+  if (normed != nullptr) {
+    ss = block_sum(ss, scratch);                 // (its barriers also publish u_s)
+    const float inv = rsqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      normed[t * width + i] = from_f<T>(u_s[i] * inv * gain[i]);
   }
 }
 
@@ -126,13 +146,38 @@ EK_EXPORT int ek_hc_broadcast(float* streams, const float* x, int n_tokens, int 
 #define EK_INSTANTIATE(SUFFIX, T)                                                                   \
   EK_EXPORT int ek_hc_step_##SUFFIX(float* streams, const void* y, const float* write_mix,          \
                                     const float* write_out, const float* read_in, float* u,         \
-                                    int n_tokens, int n, int width, cudaStream_t stream) {          \
+                                    int n_tokens, int n, int width, const float* gain, float eps,   \
+                                    void* normed, cudaStream_t stream) {                            \
     using namespace ek;                                                                             \
     if (n_tokens <= 0) return 0;                                                                    \
-    if (n < 1 || n > kMaxStreams || width <= 0 || (y && (!write_mix || !write_out)))                \
+    if (n < 1 || n > kMaxStreams || width <= 0 || (y && (!write_mix || !write_out)) ||              \
+        (normed && !gain))                                                                          \
       return EK_ERR_ARG;                                                                            \
-    hc_step_kernel<T><<<n_tokens, 256, 0, stream>>>(streams, (const T*)y, write_mix, write_out,     \
-                                                    read_in, u, n, width);                          \
+    const size_t smem = normed ? (size_t)width * sizeof(float) : 0;                                 \
+    if (smem > 200 * 1024) return EK_ERR_ARG;                                                       \
+    if (smem > 40 * 1024) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(hc_step_kernel<T, 2>,                                    \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e == cudaSuccess)                                                                         \
+        e = cudaFuncSetAttribute(hc_step_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                        \
+      if (e == cudaSuccess)                                                                         \
+        e = cudaFuncSetAttribute(hc_step_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                        \
+      if (e != cudaSuccess) return (int)e;                                                          \
+    }                                                                                               \
+    if (n <= 2)                                                                                     \
+      hc_step_kernel<T, 2><<<n_tokens, 256, smem, stream>>>(streams, (const T*)y, write_mix,        \
+                                                            write_out, read_in, u, n, width, gain,  \
+                                                            eps, (T*)normed);                       \
+    else if (n <= 4)                                                                                \
+      hc_step_kernel<T, 4><<<n_tokens, 256, smem, stream>>>(streams, (const T*)y, write_mix,        \
+                                                            write_out, read_in, u, n, width, gain,  \
+                                                            eps, (T*)normed);                       \
+    else                                                                                            \
+      hc_step_kernel<T, 8><<<n_tokens, 256, smem, stream>>>(streams, (const T*)y, write_mix,        \
+                                                            write_out, read_in, u, n, width, gain,  \
+                                                            eps, (T*)normed);                       \
     EK_RETURN_LAUNCH_STATUS();                                                                      \
   }
 

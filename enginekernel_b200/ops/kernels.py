@@ -960,7 +960,7 @@ def decode_advance(sampled, token_ids, positions, draws, remaining, out_tokens, 
 
 # ------------------------------------------------------------------ several residual streams
 _hc_broadcast = Function("hyper", "ek_hc_broadcast", [_P, _P, c_int, c_int, c_int, _P])
-_hc_step = _per_dtype("hyper", "ek_hc_step", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P])
+_hc_step = _per_dtype("hyper", "ek_hc_step", [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P, c_float, _P, _P])
 MAX_RESIDUAL_STREAMS = 8
 
 
@@ -975,11 +975,13 @@ def hc_broadcast(streams, x, n_tokens):
     _hc_broadcast(_ptr(streams), _ptr(x), n_tokens, n, width, _stream())
 
 
-def hc_step(streams, n_tokens, y=None, write_mix=None, write_out=None, read_in=None, u=None):
+def hc_step(streams, n_tokens, y=None, write_mix=None, write_out=None, read_in=None, u=None, norm=None):
     """With ``y`` [T, W]: x_t <- sum_s write_mix[s, t] x_s + write_out[t] y for all streams at once, in
     place.  Then, with ``u`` [T, W] (32-bit): u = sum_s read_in[s] x_s (``read_in`` None: the plain
-    sum).  Coefficients are 32-bit device tensors."""
-    _need_cuda(streams, y, write_mix, write_out, read_in, u)
+    sum).  With ``norm=(gain, eps, normed)``: normed [T, W] (an activation type) = gain * u * rsqrt(mean(u^2)
+    + eps), with or without ``u`` itself.  Coefficients and gain are 32-bit device tensors."""
+    gain, eps, normed = norm if norm is not None else (None, 0.0, None)
+    _need_cuda(streams, y, write_mix, write_out, read_in, u, gain, normed)
     _need(streams.dtype == torch.float32 and streams.is_contiguous() and streams.dim() == 3,
           "hc_step: streams [T, n, W] in 32-bit")
     n, width = streams.shape[1], streams.shape[2]
@@ -991,13 +993,17 @@ def hc_step(streams, n_tokens, y=None, write_mix=None, write_out=None, read_in=N
                         and write_out is not None), "hc_step: y [T, W] with its coefficients")
     _need(u is None or (u.dtype == torch.float32 and u.is_contiguous() and u.shape[-1] == width),
           "hc_step: u [T, W] in 32-bit")
-    dtype = y.dtype if y is not None else torch.float32
+    _need(normed is None or (normed.is_contiguous() and normed.shape[-1] == width and gain.dtype == torch.float32
+                             and gain.numel() == width and (y is None or y.dtype == normed.dtype)),
+          "hc_step: normed [T, W] in y's type, 32-bit gain [W]")
+    dtype = y.dtype if y is not None else (normed.dtype if normed is not None else torch.float32)
     if lib.recording():
         lib.annotate(bytes=n_tokens * width * (4 * n * (2 if y is not None else 1)
                                                + (y.element_size() if y is not None else 0)
-                                               + (4 if u is not None else 0)))
+                                               + (4 if u is not None else 0)
+                                               + (normed.element_size() if normed is not None else 0)))
     _hc_step[dtype](_ptr(streams), _ptr(y), _ptr(write_mix), _ptr(write_out), _ptr(read_in), _ptr(u),
-                    n_tokens, n, width, _stream())
+                    n_tokens, n, width, _ptr(gain), float(eps), _ptr(normed), _stream())
 
 
 # ------------------------------------------------------------------ latent attention

@@ -10,7 +10,8 @@ After the last layer the model's stream is the sum of the copies.  Parameters: `
 ``hidden_size``.  Tensors: ``in1`` [n], ``out1`` [n], ``mix1`` [n, n] (indexed [from, to]) for the
 mixer and ``in2``, ``out2``, ``mix2`` for the feed-forward (absent in a layer without one).
 Norms: ``pre_mixer``, ``pre_feed_forward``.  The copies live in 32-bit, [T, n, hidden]; the write of
-one sublayer and the read of the next are one kernel.
+one sublayer, the read of the next and - for a norm that is gain * u * rsqrt(mean(u^2) + eps) over the
+row (``Norm.deferrable``) - that norm are one kernel; any other norm is called on the mixture.
 """
 
 from __future__ import annotations
@@ -78,21 +79,31 @@ class HyperConnectionBlock(Block):
         self._step(streams, pending, None, x, ctx)
         return x, None
 
-    def _step(self, streams, pending: Optional[StreamWrite], read_in, u, ctx):
-        if pending is None:
-            kernels.hc_step(streams, ctx.n_tokens, read_in=read_in, u=u)
-        else:
-            kernels.hc_step(streams, ctx.n_tokens, y=pending.y, write_mix=pending.mix, write_out=pending.out,
-                            read_in=read_in, u=u)
+    def _step(self, streams, pending: Optional[StreamWrite], read_in, u, ctx, norm=None):
+        kw = dict(read_in=read_in, u=u, norm=norm)
+        if pending is not None:
+            kw.update(y=pending.y, write_mix=pending.mix, write_out=pending.out)
+        kernels.hc_step(streams, ctx.n_tokens, **kw)
+
+    def _read_normed(self, streams, pending, read_in, norm_part, ctx):
+        """The write of ``pending``, the read with ``read_in`` and ``norm_part`` of what was read."""
+        spec = norm_part.deferrable()
+        if spec is not None:
+            gain, eps = spec
+            normed = ctx.workspace.get("normed", (ctx.n_tokens, self.hidden), self.dtype)
+            self._step(streams, pending, read_in, None, ctx, norm=(gain, float(eps), normed))
+            return normed
+        u = ctx.workspace.get("stream_read", (ctx.n_tokens, self.hidden), torch.float32)
+        self._step(streams, pending, read_in, u, ctx)
+        return norm_part.forward(u, ctx)
 
     def forward(self, streams, pending, ctx, entry, writes_cache=True):
-        t, c = ctx.n_tokens, self.coef
-        u = ctx.workspace.get("stream_read", (t, self.hidden), torch.float32)
-        self._step(streams, pending, c["in1"], u, ctx)
-        y = self.mixer.forward(self.norms["pre_mixer"].forward(u, ctx), ctx, entry, writes_cache)
+        c = self.coef
+        a = self._read_normed(streams, pending, c["in1"], self.norms["pre_mixer"], ctx)
+        y = self.mixer.forward(a, ctx, entry, writes_cache)
         pending = StreamWrite(y, c["mix1"], c["out1"])
         if self.feed_forward is None:
             return pending
-        self._step(streams, pending, c["in2"], u, ctx)
-        y = self.feed_forward.forward(self.norms["pre_feed_forward"].forward(u, ctx), ctx)
+        a = self._read_normed(streams, pending, c["in2"], self.norms["pre_feed_forward"], ctx)
+        y = self.feed_forward.forward(a, ctx)
         return StreamWrite(y, c["mix2"], c["out2"])

@@ -52,6 +52,16 @@ def test_residual_streams_read_and_write(dtype, n, width, tokens):
     got2 = xs.clone()
     k.hc_step(got2, tokens, y=y, write_mix=mix, write_out=w_out, u=u)               # write, then the plain sum
     assert rel(u, want.sum(1)) <= 1e-6
+    gain, normed = 1 + 0.2 * rnd(width, seed=7), torch.full((tokens, width), 7.0, dtype=dtype, device=DEV)
+    for with_u in (True, False):                                                    # ... and the norm of what was read
+        got3, u3 = xs.clone(), torch.full((tokens, width), 7.0, device=DEV)
+        k.hc_step(got3, tokens, y=y, write_mix=mix, write_out=w_out, read_in=w_in, u=u3 if with_u else None,
+                  norm=(gain, 1e-5, normed))
+        assert rel(got3, want) <= 1e-6
+        assert rel(normed, plain.stream_norm(plain.streams_read(want, w_in.cpu()), gain.cpu(), 1e-5)) <= TOL[dtype]
+        assert (rel(u3, plain.streams_read(want, w_in.cpu())) <= 1e-6) if with_u else bool((u3 == 7.0).all())
+    k.hc_step(xs.clone(), tokens, read_in=w_in, norm=(gain, 1e-5, normed))          # read and norm alone
+    assert rel(normed, plain.stream_norm(plain.streams_read(xs.double().cpu(), w_in.cpu()), gain.cpu(), 1e-5)) <= TOL[dtype]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
