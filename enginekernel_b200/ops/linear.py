@@ -68,7 +68,7 @@ def pair_product_wins(out, x, w, m, epilogue) -> bool:
     return pair_fill(m, n_tiles, x.device) >= PAIR_MIN_FILL
 
 
-def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None, image=None):
+def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None, image=None, wide_f32="own"):
     """``x`` [M, K] (dense rows), ``w`` [N, K] -> [M, N] from the step's workspace.
 
     ``x`` may be a :class:`~enginekernel_b200.parts.base.DeferredNorm` (the product scales its
@@ -78,7 +78,11 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None, image=
     product adds its 32-bit result to ``stream`` and None is returned (nothing left to add: the
     norm is called without ``add``).  Otherwise the plain result comes back.
     ``image="extended"``: few-row bfloat16 products go through the compiled image that also holds the
-    extended q/k/v epilogue (see :meth:`~enginekernel_b200.parts.base.Mixer.product_image`)."""
+    extended q/k/v epilogue (see :meth:`~enginekernel_b200.parts.base.Mixer.product_image`).
+    ``wide_f32="library"``: a bfloat16 product of many rows with a 32-bit result goes to the library (the
+    same 32-bit accumulators, stored as they are) instead of this package's one-block tcgen05 form, which
+    reaches three quarters of the library's speed at best: for projections inside a layer, where a prompt
+    pays for it in every layer (the logits, once a step, keep the package's kernel)."""
     epi_bf16 = kernels.EPI_BF16_EXTENDED if image == "extended" else kernels.EPI_BF16
     from ..parts.base import DeferredNorm
     row_scale = None
@@ -129,6 +133,8 @@ def linear(x, w, ctx, name: str, n_rows=None, out_dtype=None, defer=None, image=
         return out
     if m <= SMALL_ROWS:
         kernels.gemm_tc_bf16(out, x, w, epi if want_f32 else epi_bf16, n_rows=m, swap=True, row_scale=row_scale)
+    elif want_f32 and wide_f32 == "library":
+        _library_product_f32(x[:m], w, out)
     elif want_f32:
         # 32-bit logits for many rows: 128 x 128 tiles with the accumulator stored as it is
         kernels.gemm_tc_bf16(out, x, w, epi, n_rows=m, swap=False)
@@ -149,6 +155,17 @@ def _library_product_add(stream, x, w):
         lib.record_library_call(f"library_addmm[{n}x{k}]",
                                 lambda: torch.addmm(stream, x, w.t(), out_dtype=torch.float32, out=stream),
                                 bytes=x.element_size() * (m * k + n * k) + 8 * m * n, flops=2 * m * n * k)
+
+
+def _library_product_f32(x, w, out):
+    """out (32-bit) = x . w^T for bfloat16 operands by the library: 32-bit accumulators, not rounded."""
+    torch.mm(x, w.t(), out_dtype=torch.float32, out=out[:x.shape[0]])
+    if lib.recording():
+        m, k = x.shape
+        n = w.shape[0]
+        lib.record_library_call(f"library_mm_f32[{n}x{k}]",
+                                lambda: torch.mm(x, w.t(), out_dtype=torch.float32, out=out[:m]),
+                                bytes=2 * (m * k + n * k) + 4 * m * n, flops=2 * m * n * k)
 
 
 def _library_product(x, w, out):

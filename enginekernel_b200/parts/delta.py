@@ -78,8 +78,11 @@ class ChannelDelta(Mixer):
             raise ValueError("channel_delta: the inner sizes of a1/a2 or g1/g2 disagree")
         self.rank_a, self.rank_g = a1.shape[0], g1.shape[0]
         # one product for everything that reads the input: [q | k | v | beta | a1 | g1]
-        self.w_in = torch.cat([tensors[w["q"]], tensors[w["k"]], tensors[w["v"]], tensors[w["b"]], a1, g1], 0) \
-            .to(self.dtype).contiguous()
+        # (zero rows up to a multiple of 64: the library's product of many rows is much slower on a ragged count)
+        rows = [tensors[w["q"]], tensors[w["k"]], tensors[w["v"]], tensors[w["b"]], a1, g1]
+        n = sum(r.shape[0] for r in rows)
+        rows.append(torch.zeros((-n % 64, self.hidden), dtype=a1.dtype, device=a1.device))
+        self.w_in = torch.cat(rows, 0).to(self.dtype).contiguous()
         self.conv_w = torch.cat([tensors[w["q_conv"]], tensors[w["k_conv"]], tensors[w["v_conv"]]], 0) \
             .to(f32).contiguous()
         self.a2t = a2.to(f32).t().contiguous()              # [ra, H d]: neighbouring channels side by side
@@ -96,7 +99,7 @@ class ChannelDelta(Mixer):
         t, ws, f32 = ctx.n_tokens, ctx.workspace, torch.float32
         nh, g, d, e = self.num_heads, self.num_kv_heads, self.head_dim, self.v_dim
         state = entry.state                                  # [slots, values] 32-bit
-        proj = linear(x, self.w_in, ctx, "delta_in", n_rows=t, out_dtype=f32)
+        proj = linear(x, self.w_in, ctx, "delta_in", n_rows=t, out_dtype=f32, wide_f32="library")
         qn = ws.get("delta_q", (t, g * d), f32)
         kn = ws.get("delta_k", (t, g * d), f32)
         vc = ws.get("delta_v", (t, nh * e), f32)

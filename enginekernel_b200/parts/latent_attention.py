@@ -81,7 +81,10 @@ class LatentAttention(Mixer):
     def load(self, tensors):
         w = self.spec.weights
         nh, d, e, c = self.num_heads, self.head_dim, self.v_dim, self.kv_rank
-        self.w_down = torch.cat([tensors[w["dq"]], tensors[w["dkv"]]], 0).to(self.dtype).contiguous()
+        down = [tensors[w["dq"]], tensors[w["dkv"]]]          # (zero rows up to a multiple of 64, for the library's product)
+        n = down[0].shape[0] + down[1].shape[0]
+        down.append(torch.zeros((-n % 64, self.hidden), dtype=down[0].dtype, device=down[0].device))
+        self.w_down = torch.cat(down, 0).to(self.dtype).contiguous()
         self.w_uq = tensors[w["uq"]].to(self.dtype).contiguous()
         # [heads, in, out] for the per-head products: the absorbed query reads W_uk transposed,
         # which is how it is stored ([H d, c] = [heads, d, c]); W_uv [H e, c] is turned once
@@ -103,7 +106,7 @@ class LatentAttention(Mixer):
         rot_dims = pos.rotary_dim if pos is not None else 0
         cos, sin = (pos.cos, pos.sin) if pos is not None else (None, None)
         # both down-projections in one product, kept in 32-bit for the norms and the rotation
-        down = linear(x, self.w_down, ctx, "latent_down", n_rows=t, out_dtype=torch.float32)
+        down = linear(x, self.w_down, ctx, "latent_down", n_rows=t, out_dtype=torch.float32, wide_f32="library")
         cq = ws.get("latent_cq", (t, a), self.dtype)
         kernels.latent_prepare(cq, down, t, self.gain_q, self.gain_kv, self.eps, cos, sin, rot_dims,
                                ctx.positions, ctx.token_slot, entry.k_pages, entry.block_table, a, c, r,

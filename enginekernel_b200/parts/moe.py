@@ -69,7 +69,7 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         t, ws, top = ctx.n_tokens, ctx.workspace, self.top
         pairs = t * top
-        logits = linear(x, self.w_router, ctx, "router_logits", n_rows=t, out_dtype=torch.float32)
+        logits = linear(x, self.w_router, ctx, "router_logits", n_rows=t, out_dtype=torch.float32, wide_f32="library")
         chosen = ws.get("moe_chosen", (t, top), torch.int32)
         weight = ws.get("moe_weight", (t, top), torch.float32)
         kernels.moe_route(chosen, weight, logits, t, self.groups, self.keep, top, self.scale)
