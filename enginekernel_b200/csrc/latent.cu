@@ -7,10 +7,10 @@
 //     score_h(i, j) = (W_uk,h^T q_h,flat)(i) . c(j) + q_h,rot(i) . r(j),
 //     out_h(i)      = W_uv,h sum_j p_h(i, j) c(j),
 // that is: attention with ONE key head whose keys and values are both the cached rows, H query
-// heads of size D, followed by a product per head.  Three kernels:
+// heads of size D, followed by a product per head.  Two kernels:
 //   latent_prepare   norms of the two latents (32-bit), rotation of r, cache write, per token
-//   latent_absorb    q_abs = [W_uk,h^T q_h,flat ; rot(q_h,rot) ; 0] per token and head
-//   head_linear      out[t, h, :] = W_h in[t, h, :] (the value up-projection)
+//   head_linear      out[t, h, :] = W_h in[t, h, :] per head: the value up-projection, and - with the
+//                    rotated tail - the absorbed query [W_uk,h^T q_h,flat ; rot(q_h,rot) ; 0]
 // Norms, angles and rotations are computed in 32-bit; T is the activation / cache type.
 #include "common.cuh"
 

@@ -140,7 +140,7 @@ moe_plan_kernel(int* __restrict__ sorted_pair, int* __restrict__ tiles, int* __r
   }
 }
 
-constexpr int ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3;
+constexpr int ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3;      // 0: none
 
 __device__ __forceinline__ float activate(float z, int act) {
   if (act == ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }

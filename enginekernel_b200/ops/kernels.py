@@ -1080,7 +1080,6 @@ def head_linear(out, x, w, n_tokens, heads, n_in, n_out, rot=None):
 
 
 # ------------------------------------------------------------------ delta rule with a decay per key channel
-_delta_state_rows = Function("delta", "ek_delta_state_rows", [c_int], check_status=False)
 _delta_prepare = Function("delta", "ek_delta_prepare",
                           [_P, _P, _P, _P, _P, c_int, _P, _P, c_longlong, c_longlong, _P, _P,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P])
